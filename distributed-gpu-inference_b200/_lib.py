@@ -142,15 +142,15 @@ MIXER_SIGNATURES = {
         c_int, [c_void_p, c_int64, c_void_p, c_float, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200_mixed_paged_attn": (
         c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
-                c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_float, c_int,
-                c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int, c_int, c_float,
+                c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_mixed_prompt_attn_supported": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "b200_mixed_prompt_attn_splits": (c_int, [c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int]),
     "b200_mixed_prompt_attn_workspace": (c_size_t, [c_int, c_int, c_int, c_int]),
     "b200_mixed_prompt_attn": (
         c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
-                c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p, c_int, c_int,
-                c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
+                c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_void_p, c_int,
+                c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
     "b200_causal_conv_silu": (
         c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                 c_void_p]),
@@ -159,6 +159,27 @@ MIXER_SIGNATURES = {
                 c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p]),
     "b200_head_rmsnorm_gated": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_float, c_int64, c_int, c_int, c_int, c_void_p]),
+    # side-by-side mixers, post-norm sublayers, grouped softmax routing (csrc/b200_parallel_ops.cu)
+    "b200_qknorm_rotary_append": (
+        c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int,
+                c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int,
+                c_void_p]),
+    "b200_retention_scan": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
+                c_int, c_int, c_int, c_void_p]),
+    "b200_head_norm_act_gate": (
+        c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_float, c_int64, c_int, c_int,
+                c_int, c_void_p]),
+    "b200_branch_postnorm_residual": (
+        c_int, [c_void_p, c_void_p, c_int64, c_int, c_float, c_void_p, c_int64, c_float, c_void_p, c_void_p, c_void_p,
+                c_float, c_int, c_int, c_int, c_void_p]),
+    "b200_cast_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p]),
+    "b200_softmax_group_topk": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
+    "b200_weighted_expert_combine": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int,
+                c_void_p]),
 }
 
 _lock = threading.Lock()
@@ -214,7 +235,7 @@ def _build_mixers() -> None:
         fcntl.flock(lock, fcntl.LOCK_EX)
         if os.path.exists(MIXER_LIB_PATH):
             return
-        proc = subprocess.run(["make", "-j2", "-C", csrc, "mixers"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+        proc = subprocess.run(["make", "-j3", "-C", csrc, "mixers"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
         if proc.returncode != 0 or not os.path.exists(MIXER_LIB_PATH):
             raise B200LibraryError("building libb200_mixers.so failed:\n" + proc.stdout.decode(errors="replace")[-4000:])
 

@@ -10,8 +10,9 @@
 //                               attention are the same cached rows)
 //   mixed-head paged attention  softmax attention of packed query rows over the paged cache with (all optional) a
 //                               sliding window that keeps the first tokens of the sequence, a learned sink logit in
-//                               the denominator, a head-mixing matrix applied to the scores before the softmax, the
-//                               inverse value rotation of the output and a per-head sigmoid gate
+//                               the denominator, a head-mixing matrix applied to the scores before the softmax, a tanh
+//                               soft cap on the scores, the inverse value rotation of the output and a per-head
+//                               sigmoid gate
 //   short causal convolution    per channel over a sequence's tokens, then SiLU; the last taps - 1 inputs of every
 //                               live sequence are carried in a slot pool
 //   gated delta rule            S <- diag(g) S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q  with a decay per
@@ -257,6 +258,7 @@ struct AttnArgs {
   const float* talk; const float* sink;
   float scale; int window, keep_first, unrotate, interleaved; double rot_base;
   int H, G, dk, dv, block_size;
+  float softcap;   // > 0: score <- softcap * tanh(score / softcap), after the head mixing and before the mask
 };
 
 constexpr int kAttnWarpsRow = 4;
@@ -349,6 +351,7 @@ mixed_paged_attn_kernel(const AttnArgs A) {
           } else {
             t = raw_w[hl * 32 + lane];
           }
+          if (A.softcap > 0.f) t = A.softcap * tanhf(t / A.softcap);
         }
         const float m_new = fmaxf(m_r[hl], warp_max(t));
         if (m_new != -INFINITY) {
@@ -660,6 +663,7 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
           for (int e = 0; e < 2; ++e) {
             const int j = j0 + nt * 8 + qc + e;
             const bool ok = row_ok && j <= p && (A.window <= 0 || p - j < A.window || j < A.keep_first);
+            if (A.softcap > 0.f) s[nt][2 * half + e] = A.softcap * tanhf(s[nt][2 * half + e] / A.softcap);
             if (!ok) s[nt][2 * half + e] = -INFINITY;
             mx = fmaxf(mx, s[nt][2 * half + e]);
           }
@@ -1249,9 +1253,9 @@ int b200_norm_append(const void* x, int64_t x_stride, const void* weight, float 
 int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q, int64_t q_tok_stride,
                           int64_t q_head_stride, const void* gate, int64_t gate_stride, const void* k_pool,
                           const void* v_pool, const int32_t* block_tables, int table_stride, const int32_t* tok_row,
-                          const int32_t* tok_pos, int n_tok, const float* talk, const float* sink, float scale, int window,
-                          int keep_first, int unrotate, int interleaved, float rot_base, int H, int G, int dk, int dv,
-                          int block_size, int dtype, void* stream) {
+                          const int32_t* tok_pos, int n_tok, const float* talk, const float* sink, float scale,
+                          float softcap, int window, int keep_first, int unrotate, int interleaved, float rot_base, int H,
+                          int G, int dk, int dv, int block_size, int dtype, void* stream) {
   if (n_tok < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || block_size <= 0)
     return fail(B200_EINVAL, "b200_mixed_paged_attn: bad sizes");
   if (dv > 512) return fail(B200_ESHAPE, "b200_mixed_paged_attn: value size %d beyond 512", dv);
@@ -1260,7 +1264,7 @@ int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_st
     return fail(B200_EINVAL, "b200_mixed_paged_attn: null pointer");
   AttnArgs A{out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride, k_pool, v_pool,
              block_tables, table_stride, tok_row, tok_pos, talk, sink, scale, window, keep_first, unrotate, interleaved,
-             static_cast<double>(rot_base), H, G, dk, dv, block_size};
+             static_cast<double>(rot_base), H, G, dk, dv, block_size, softcap};
   const int dvc = dv <= 64 ? 2 : (dv <= 128 ? 4 : (dv <= 256 ? 8 : 16));
   const int hp = dvc <= 4 ? 8 : (dvc == 8 ? 4 : 2);
   const int nhs = talk ? H : std::min(hp, H);
@@ -1309,8 +1313,9 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
                            int64_t q_head_stride, const void* gate, int64_t gate_stride, const void* k_pool,
                            const void* v_pool, const int32_t* block_tables, int table_stride, const int32_t* tiles,
                            int n_tiles, const int32_t* tok_pos, int n_tok, const float* talk, const float* sink,
-                           float scale, int window, int keep_first, const float* value_rot, int interleaved, int H, int G,
-                           int dk, int dv, int block_size, int n_splits, float* workspace, int dtype, void* stream) {
+                           float scale, float softcap, int window, int keep_first, const float* value_rot, int interleaved,
+                           int H, int G, int dk, int dv, int block_size, int n_splits, float* workspace, int dtype,
+                           void* stream) {
   if (n_tiles < 0 || n_tok < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || block_size <= 0 || n_splits < 1 ||
       n_splits > 64)
     return fail(B200_EINVAL, "b200_mixed_prompt_attn: bad sizes");
@@ -1324,7 +1329,7 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
     return fail(B200_ESHAPE, "b200_mixed_prompt_attn: sizes off the tensor-core grid (dk %d, dv %d)", dk, dv);
   AttnArgs A{out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride, k_pool, v_pool,
              block_tables, table_stride, nullptr, tok_pos, talk, sink, scale, window, keep_first, value_rot != nullptr,
-             interleaved, 0.0, H, G, dk, dv, block_size};
+             interleaved, 0.0, H, G, dk, dv, block_size, softcap};
   const dim3 grid(n_tiles, (H + kTcWarps * plan.hw - 1) / (kTcWarps * plan.hw), n_splits);
   return hybrid_by_dtype(dtype, "b200_mixed_prompt_attn", [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;

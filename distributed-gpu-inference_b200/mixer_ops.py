@@ -392,12 +392,13 @@ def mixed_paged_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tens
                           block_tables: torch.Tensor, tok_row: torch.Tensor, tok_pos: torch.Tensor, scale: float,
                           talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, window: int = 0,
                           keep_first: int = 0, unrotate_base: Optional[float] = None, interleaved: bool = False,
-                          gate: Optional[torch.Tensor] = None) -> None:
+                          gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
     """Softmax attention of packed query rows over the paged cache.  ``q`` and ``out`` are 3-D ``[n, H, dk | dv]``
     VIEWS with a contiguous last dimension (any token / head strides); ``talk`` fp32 ``[H, H]`` mixes the heads'
     scores before the softmax, ``sink`` fp32 ``[H]`` adds exp(sink) to the denominator, ``window`` > 0 limits a
     position to its last ``window`` tokens plus the sequence's first ``keep_first``, ``unrotate_base`` turns the
-    output back by the position over the value width, ``gate`` ``[n, H]`` is a sigmoid gate per head."""
+    output back by the position over the value width, ``gate`` ``[n, H]`` is a sigmoid gate per head, ``softcap`` > 0
+    bounds the scores by ``softcap * tanh(score / softcap)`` before the mask."""
     _need_cuda(out, q, k_pool, v_pool, block_tables, tok_row, tok_pos)
     nb, G, bs, dk = k_pool.shape
     dv = v_pool.shape[3]
@@ -417,8 +418,8 @@ def mixed_paged_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tens
     rc = _lib_().b200_mixed_paged_attn(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0), q.stride(1),
                                        _ptr(gate), _rows2(gate) if gate is not None else 0, k_pool.data_ptr(),
                                        v_pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), tok_row.data_ptr(),
-                                       tok_pos.data_ptr(), n, _ptr(talk), _ptr(sink), float(scale), int(window),
-                                       int(keep_first), int(unrotate_base is not None), int(interleaved),
+                                       tok_pos.data_ptr(), n, _ptr(talk), _ptr(sink), float(scale), float(softcap),
+                                       int(window), int(keep_first), int(unrotate_base is not None), int(interleaved),
                                        float(unrotate_base or 0.0), H, G, dk, dv, bs, DTYPE_ID[q.dtype], _stream())
     _lib.check_mixers(rc, "b200_mixed_paged_attn")
 
@@ -437,7 +438,7 @@ def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Ten
                            block_tables: torch.Tensor, tiles: torch.Tensor, tok_pos: torch.Tensor, scale: float,
                            talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, window: int = 0,
                            keep_first: int = 0, value_rot: Optional[torch.Tensor] = None, interleaved: bool = False,
-                           gate: Optional[torch.Tensor] = None, max_context: int = 0) -> None:
+                           gate: Optional[torch.Tensor] = None, max_context: int = 0, softcap: float = 0.0) -> None:
     """``mixed_paged_attention`` on the tensor cores for prompt portions and decoded tokens alike (16-bit dtypes, see
     ``mixed_prompt_attention_supported``).  ``tiles`` int32 ``[n_tiles, 3]``: up to ``PROMPT_TILE_TOKENS`` consecutive
     tokens of one sequence each, together covering every row of ``q``; ``value_rot``: the table ``rotary_kv_append``
@@ -472,8 +473,9 @@ def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Ten
     rc = lib.b200_mixed_prompt_attn(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0), q.stride(1),
                                     _ptr(gate), _rows2(gate) if gate is not None else 0, k_pool.data_ptr(),
                                     v_pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), tiles.data_ptr(),
-                                    tiles.shape[0], tok_pos.data_ptr(), n, _ptr(talk), _ptr(sink), float(scale), int(window),
-                                    int(keep_first), _ptr(value_rot), int(interleaved), H, G, dk, dv, bs, int(splits),
+                                    tiles.shape[0], tok_pos.data_ptr(), n, _ptr(talk), _ptr(sink), float(scale),
+                                    float(softcap), int(window), int(keep_first), _ptr(value_rot), int(interleaved), H, G,
+                                    dk, dv, bs, int(splits),
                                     _ptr(ws), DTYPE_ID[q.dtype], _stream())
     _lib.check_mixers(rc, "b200_mixed_prompt_attn")
 
@@ -541,4 +543,188 @@ def head_rmsnorm_gated(x: torch.Tensor, weight: torch.Tensor, gate: Optional[tor
                                          _rows2(gate) if gate is not None else 0, float(eps), n, H, dv,
                                          DTYPE_ID[weight.dtype], _stream())
     _lib.check_mixers(rc, "b200_head_rmsnorm_gated")
+    return out
+
+
+# ---- side-by-side mixers, post-norm sublayers, grouped softmax routing (csrc/b200_parallel_ops.cu) ---------------------
+def _check_seqs(seqs: torch.Tensor) -> None:
+    if seqs.dtype != torch.int32 or seqs.dim() != 2 or seqs.shape[1] != 4 or not seqs.is_contiguous():
+        raise ValueError("seqs must be contiguous int32 [n_seqs, 4]")
+
+
+@_timed
+def qknorm_rotary_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_norm: Optional[torch.Tensor],
+                         k_norm: Optional[torch.Tensor], eps: float, freqs: Optional[torch.Tensor], k_pool: torch.Tensor,
+                         v_pool: torch.Tensor, slot_mapping: torch.Tensor, tok_pos: torch.Tensor, H: int,
+                         interleaved: bool = True) -> None:
+    """Per-head RMS norm of q (in place) and k (weights ``[dk]``, None: no norm), rotary positions over the first
+    ``2 * len(freqs)`` dimensions of every head with angle ``pos * freqs[i]`` (``freqs`` float64 on the device), k and v
+    stored in the pools at ``slot_mapping``."""
+    _need_cuda(q, k, v, k_pool, v_pool, slot_mapping, tok_pos)
+    nb, G, bs, dk = k_pool.shape
+    dv = v_pool.shape[3]
+    n = q.shape[0]
+    if q.shape[1] != H * dk or k.shape != (n, G * dk) or v.shape != (n, G * dv):
+        raise ValueError("q / k / v do not match the pools")
+    if slot_mapping.dtype != torch.int64 or tok_pos.dtype != torch.int32:
+        raise TypeError("slot_mapping is int64, tok_pos int32")
+    for w in (q_norm, k_norm):
+        if w is not None and (w.numel() != dk or w.dtype != q.dtype or not w.is_contiguous()):
+            raise ValueError("norm weights are contiguous [dk] in the activations' dtype")
+    rot_dims = 0
+    if freqs is not None:
+        if freqs.dtype != torch.float64 or not freqs.is_contiguous() or not freqs.is_cuda:
+            raise ValueError("freqs is a contiguous float64 tensor on the device")
+        rot_dims = 2 * freqs.numel()
+    rc = _lib_().b200_qknorm_rotary_append(q.data_ptr(), _rows2(q), k.data_ptr(), _rows2(k), v.data_ptr(), _rows2(v),
+                                           _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(freqs), rot_dims, int(interleaved),
+                                           k_pool.data_ptr(), v_pool.data_ptr(), slot_mapping.data_ptr(),
+                                           tok_pos.data_ptr(), n, H, G, dk, dv, bs, nb, DTYPE_ID[k_pool.dtype], _stream())
+    _lib.check_mixers(rc, "b200_qknorm_rotary_append")
+
+
+@_timed
+def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, k_scale: float,
+                   state: torch.Tensor, seqs: torch.Tensor) -> torch.Tensor:
+    """Fixed-decay linear attention over each sequence's tokens: ``S <- decay[h] S + (k_scale k) v^T``, ``o = S^T q``;
+    ``state`` fp32 ``[slots, H, dk, dv]`` is read (unless the sequence is fresh) and written back.  ``q / k [n, H*dk]``
+    and ``v [n, H*dv]`` are column slices of ONE tensor.  Returns fp32 ``[n, H, dv]``."""
+    _need_cuda(q, k, v, decay, state, seqs)
+    n = q.shape[0]
+    _, H, dk, dv = state.shape
+    if q.shape[1] != H * dk or k.shape != q.shape or v.shape != (n, H * dv):
+        raise ValueError("projections do not match the state's shape")
+    stride = _rows2(q)
+    if n > 1 and (k.stride(0) != stride or v.stride(0) != stride):
+        raise ValueError("q, k and v must share a row stride")
+    if state.dtype != torch.float32 or not state.is_contiguous():
+        raise TypeError("the recurrent state is contiguous fp32")
+    if decay.dtype != torch.float32 or decay.numel() != H or not decay.is_contiguous():
+        raise ValueError("decay is contiguous fp32 [H]")
+    _check_seqs(seqs)
+    o = torch.empty((n, H, dv), dtype=torch.float32, device=q.device)
+    rc = _lib_().b200_retention_scan(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), stride, decay.data_ptr(),
+                                     float(k_scale), state.data_ptr(), seqs.data_ptr(), seqs.shape[0], H, dk, dv,
+                                     DTYPE_ID[q.dtype], _stream())
+    _lib.check_mixers(rc, "b200_retention_scan")
+    return o
+
+
+@_timed
+def head_norm_act_gate(x: torch.Tensor, weight: Optional[torch.Tensor], gate: Optional[torch.Tensor], eps: float,
+                       dtype: torch.dtype, gate_act: str = "silu", out_scale: float = 1.0,
+                       out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 ``[n, H, dv]`` -> ``x * rsqrt(mean(x^2) + eps) [* weight] * act(gate) * out_scale`` as ``[n, H*dv]`` in
+    ``dtype``; ``gate [n, H*dv]`` holds pre-activations, ``gate_act`` is ``"sigmoid"`` or ``"silu"``; ``out`` may be a
+    column slice of a wider buffer."""
+    _need_cuda(x)
+    n, H, dv = x.shape
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise ValueError("x must be contiguous fp32 [n, H, dv]")
+    if weight is not None and (weight.numel() != dv or weight.dtype != dtype):
+        raise ValueError("weight must be [dv] in the output dtype")
+    if gate is not None and (tuple(gate.shape) != (n, H * dv) or gate.dtype != dtype):
+        raise ValueError("gate must be [n, H*dv] in the output dtype")
+    if out is None:
+        out = torch.empty((n, H * dv), dtype=dtype, device=x.device)
+    elif tuple(out.shape) != (n, H * dv) or out.dtype != dtype:
+        raise ValueError("out must be [n, H*dv] in the output dtype")
+    rc = _lib_().b200_head_norm_act_gate(out.data_ptr(), _rows2(out), x.data_ptr(), _ptr(weight), _ptr(gate),
+                                         _rows2(gate) if gate is not None else 0, {"sigmoid": 0, "silu": 1}[gate_act],
+                                         float(out_scale), float(eps), n, H, dv, DTYPE_ID[dtype], _stream())
+    _lib.check_mixers(rc, "b200_head_norm_act_gate")
+    return out
+
+
+@_timed
+def branch_postnorm_residual(x: torch.Tensor, a: torch.Tensor, sa: float, b: Optional[torch.Tensor], sb: float,
+                             w_norm: torch.Tensor, layer_scale: Optional[torch.Tensor], eps: float,
+                             want_copy: bool = True) -> Optional[torch.Tensor]:
+    """In place ``x += layer_scale * w_norm * y * rsqrt(mean(y^2) + eps)`` with ``y = sa a + sb b`` on the fp32 residual;
+    ``a`` is fp32 or of the weights' dtype, ``b`` (optional) of the weights' dtype.  With ``want_copy`` returns the new
+    ``x`` in the weights' dtype (what sublayers that read the residual itself take as GEMM input)."""
+    _need_cuda(x, a, w_norm)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2 or a.shape != x.shape:
+        raise ValueError("x must be contiguous fp32 [rows, width] and the branches of the same shape")
+    T = w_norm.dtype
+    if a.dtype not in (T, torch.float32) or (b is not None and (b.dtype != T or b.shape != x.shape)):
+        raise TypeError("a is fp32 or of the weights' dtype, b of the weights' dtype")
+    if layer_scale is not None and (layer_scale.dtype != T or layer_scale.numel() != x.shape[1]):
+        raise ValueError("layer_scale must be [width] in the weights' dtype")
+    out = torch.empty(x.shape, dtype=T, device=x.device) if want_copy else None
+    rc = _lib_().b200_branch_postnorm_residual(x.data_ptr(), a.data_ptr(), _rows2(a), int(a.dtype == torch.float32 and
+                                               T != torch.float32), float(sa), _ptr(b), _rows2(b) if b is not None else 0,
+                                               float(sb), w_norm.data_ptr(), _ptr(layer_scale), _ptr(out), float(eps),
+                                               x.shape[0], x.shape[1], DTYPE_ID[T], _stream())
+    _lib.check_mixers(rc, "b200_branch_postnorm_residual")
+    return out
+
+
+@_timed
+def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """Contiguous fp32 tensor -> the same numbers in ``dtype``."""
+    _need_cuda(x)
+    if x.dtype != torch.float32 or not x.is_contiguous():
+        raise ValueError("x must be contiguous fp32")
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    rc = _lib_().b200_cast_rows(out.data_ptr(), x.data_ptr(), x.numel(), DTYPE_ID[dtype], _stream())
+    _lib.check_mixers(rc, "b200_cast_rows")
+    return out
+
+
+@_timed
+def softmax_group_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int = 1,
+                       keep: int = 1):
+    """fp32 ``[n, E]`` router logits -> ``(ids int32 [n, top], weights fp32 [n, top])``: softmax scores, the choice by
+    score + ``correction`` inside the ``keep`` best of ``groups`` expert groups, weights = chosen scores over their
+    sum."""
+    _need_cuda(logits)
+    if logits.dtype != torch.float32 or not logits.is_contiguous() or logits.dim() != 2:
+        raise ValueError("router logits are contiguous fp32 [n, E]")
+    n, E = logits.shape
+    if correction is not None and (correction.dtype != torch.float32 or correction.numel() != E
+                                   or not correction.is_contiguous()):
+        raise ValueError("correction is contiguous fp32 [E]")
+    ids = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    w = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    rc = _lib_().b200_softmax_group_topk(ids.data_ptr(), w.data_ptr(), logits.data_ptr(), _ptr(correction), n, E, int(top),
+                                         int(groups), int(keep), _stream())
+    _lib.check_mixers(rc, "b200_softmax_group_topk")
+    return ids, w
+
+
+@_timed
+def gather_rows(h: torch.Tensor, src: torch.Tensor, top: int) -> torch.Tensor:
+    """``xs[r] = h[src[r] // top]``: rows in expert order."""
+    _need_cuda(h, src)
+    if not h.is_contiguous() or src.dtype != torch.int64:
+        raise ValueError("h contiguous, src int64")
+    xs = torch.empty((src.numel(), h.shape[1]), dtype=h.dtype, device=h.device)
+    rc = _lib_().b200_gather_rows(xs.data_ptr(), h.data_ptr(), src.data_ptr(), src.numel(), int(top), h.shape[1],
+                                  DTYPE_ID[h.dtype], _stream())
+    _lib.check_mixers(rc, "b200_gather_rows")
+    return xs
+
+
+@_timed
+def weighted_expert_combine(ys: torch.Tensor, where: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
+                            x_self: torch.Tensor, shared: Optional[torch.Tensor], n_real: int) -> torch.Tensor:
+    """fp32 ``[n, width]``: ``sum_k weights[n, k] * (ys[where[n*top + k]] if ids[n, k] < n_real else x_self[n])`` plus
+    ``shared[n]`` when given.  ``x_self`` is the fp32 row an identity expert returns."""
+    _need_cuda(ys, where, ids, weights, x_self)
+    n, top = ids.shape
+    width = x_self.shape[1]
+    if not ys.is_contiguous() or ys.shape[1] != width or where.dtype != torch.int64 or where.numel() != n * top:
+        raise ValueError("ys contiguous [rows, width], where int64 [n * top]")
+    if ids.dtype != torch.int32 or weights.dtype != torch.float32 or not ids.is_contiguous() or not weights.is_contiguous():
+        raise ValueError("ids int32 and weights fp32, contiguous [n, top]")
+    if x_self.dtype != torch.float32 or not x_self.is_contiguous() or x_self.shape[0] != n:
+        raise ValueError("x_self is contiguous fp32 [n, width]")
+    if shared is not None and (shared.shape != x_self.shape or shared.dtype != ys.dtype or not shared.is_contiguous()):
+        raise ValueError("shared rows are contiguous [n, width] in the experts' dtype")
+    out = torch.empty((n, width), dtype=torch.float32, device=ys.device)
+    rc = _lib_().b200_weighted_expert_combine(out.data_ptr(), ys.data_ptr(), where.data_ptr(), ids.data_ptr(),
+                                              weights.data_ptr(), x_self.data_ptr(), _ptr(shared), n, top, int(n_real),
+                                              width, DTYPE_ID[ys.dtype], _stream())
+    _lib.check_mixers(rc, "b200_weighted_expert_combine")
     return out

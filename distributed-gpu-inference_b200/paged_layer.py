@@ -231,7 +231,8 @@ class RaggedBatchState:
 @dataclass
 class RaggedLayerCache:
     """What a ragged layer expects in ``past_key_values[i]``: an attention layer's K / V pools (their row widths may
-    differ) or a recurrent layer's state tensor ``[slots, ...]``, plus the step's shared state."""
+    differ), a recurrent layer's state tensor ``[slots, ...]``, or both for a layer that runs the two side by side,
+    plus the step's shared state."""
 
     k_pool: Optional[torch.Tensor]
     v_pool: Optional[torch.Tensor]

@@ -60,16 +60,19 @@ class RaggedStepEngine:
         cfg = self.config
         self.kv_pools: List[Optional[KVCachePool]] = []
         self.state_pools: List[Optional[RecurrentStatePool]] = []
-        self._layer_slot: List[List[Tuple[str, int]]] = []   # per shard, per layer: ("kv" | "state", index in its pool)
+        # per shard, per layer: (index in the page pool or None, index in the state pool or None); a layer whose mixer
+        # runs an attention and a recurrence side by side keeps both
+        self._layer_slot: List[List[Tuple[Optional[int], Optional[int]]]] = []
         for sh in self.shards:
             kv_shapes, st_shapes, where = [], [], []
             for i in range(sh.start_layer, sh.end_layer):
                 kv, rs = cfg.kv_shape(i), cfg.state_shape(i)
+                if kv is None and rs is None:
+                    raise ValueError(f"layer {i} keeps neither pages nor a state")
+                where.append((len(kv_shapes) if kv is not None else None, len(st_shapes) if rs is not None else None))
                 if kv is not None:
-                    where.append(("kv", len(kv_shapes)))
                     kv_shapes.append(kv)
-                else:
-                    where.append(("state", len(st_shapes)))
+                if rs is not None:
                     st_shapes.append(rs)
             self._layer_slot.append(where)
             self.kv_pools.append(KVCachePool(num_layers=len(kv_shapes), num_heads=0, head_dim=0, block_size=block_size,
@@ -209,12 +212,11 @@ class RaggedStepEngine:
         h = up(np.asarray(ids, dtype=np.int64))
         for si, shard in enumerate(self.shards):
             handles = []
-            for kind, j in self._layer_slot[si]:
-                if kind == "kv":
-                    c = self.kv_pools[si].layer(j)
-                    handles.append(RaggedLayerCache(c.key_pool, c.value_pool, None, st))
-                else:
-                    handles.append(RaggedLayerCache(None, None, self.state_pools[si].layer(j), st))
+            for kv_j, st_j in self._layer_slot[si]:
+                c = self.kv_pools[si].layer(kv_j) if kv_j is not None else None
+                handles.append(RaggedLayerCache(c.key_pool if c is not None else None,
+                                                c.value_pool if c is not None else None,
+                                                self.state_pools[si].layer(st_j) if st_j is not None else None, st))
             if self.layer_trace is not None:
                 h = self._forward_traced(shard, h, handles)
             else:

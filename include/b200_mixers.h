@@ -145,6 +145,7 @@ int b200_norm_append(const void* x, int64_t x_stride, const void* weight, float 
 /* Softmax attention of packed query rows over the paged cache (which already holds this step's keys and values).
  *   raw(h, i, j)   = (q_ih . k_j) * scale                      k of kv head h / (H / G)
  *   score(h, i, j) = sum_g talk[h][g] raw(g, i, j)              (talk NULL: score = raw)
+ *   softcap > 0    : score <- softcap * tanh(score / softcap)
  *   visible        : j <= i and (window <= 0 or i - j < window or j < keep_first)
  *   out(i, h)      = sum_j exp(score) v_j / (sum_j exp(score) + exp(sink[h]))     (sink NULL: no extra term)
  * With unrotate, pair m of out(i, h) is turned by -pos_i * rot_base^(-2m / dv) (the inverse of the rotation the
@@ -153,9 +154,9 @@ int b200_norm_append(const void* x, int64_t x_stride, const void* weight, float 
 int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q, int64_t q_tok_stride,
                           int64_t q_head_stride, const void* gate, int64_t gate_stride, const void* k_pool,
                           const void* v_pool, const int32_t* block_tables, int table_stride, const int32_t* tok_row,
-                          const int32_t* tok_pos, int n_tok, const float* talk, const float* sink, float scale, int window,
-                          int keep_first, int unrotate, int interleaved, float rot_base, int H, int G, int dk, int dv,
-                          int block_size, int dtype, void* stream);
+                          const int32_t* tok_pos, int n_tok, const float* talk, const float* sink, float scale,
+                          float softcap, int window, int keep_first, int unrotate, int interleaved, float rot_base, int H,
+                          int G, int dk, int dv, int block_size, int dtype, void* stream);
 
 /* The same attention on the tensor cores (16-bit T; dk a multiple of 16, dv a multiple of 8 up to 256, and a shared-
  * memory budget that b200_mixed_prompt_attn_supported checks; same_pool: keys and values are one pool).  tiles: int32
@@ -175,8 +176,9 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
                            int64_t q_head_stride, const void* gate, int64_t gate_stride, const void* k_pool,
                            const void* v_pool, const int32_t* block_tables, int table_stride, const int32_t* tiles,
                            int n_tiles, const int32_t* tok_pos, int n_tok, const float* talk, const float* sink,
-                           float scale, int window, int keep_first, const float* value_rot, int interleaved, int H, int G,
-                           int dk, int dv, int block_size, int n_splits, float* workspace, int dtype, void* stream);
+                           float scale, float softcap, int window, int keep_first, const float* value_rot, int interleaved,
+                           int H, int G, int dk, int dv, int block_size, int n_splits, float* workspace, int dtype,
+                           void* stream);
 
 /* out[t, c] = silu(sum_i w[c][i] * x[t - (taps - 1 - i), c]) per sequence (SeqSpan rows); inputs before the portion
  * come from tail [slots, taps - 1, C] (fp32, oldest first), which then receives the portion's last taps - 1 inputs. */
@@ -198,6 +200,57 @@ int b200_delta_scan(float* o_raw, const void* q, const void* k, const void* v, i
  * gate T rows of H*dv (NULL: no gate), out T [n_tok, H*dv]. */
 int b200_head_rmsnorm_gated(void* out, const float* x, const void* weight, const void* gate, int64_t gate_stride, float eps,
                             int64_t n_tok, int H, int dv, int dtype, void* stream);
+
+/* ---- pieces for designs with side-by-side mixers, post-norm sublayers and grouped softmax routing ------------------ */
+
+/* Per-head RMS norm of q (in place) and k with weights q_norm / k_norm (T [dk]; NULL: no norm), then rotary positions on
+ * the first rot_dims dimensions of every head, pair (i, i + rot_dims/2) (interleaved: (2i, 2i + 1)) turned by
+ * pos * freqs[i]; freqs: rot_dims / 2 doubles ON THE DEVICE (any frequency rescaling is the caller's).  k and v go to the
+ * pools ([max_blocks, G, block_size, dk | dv]) at slot_mapping (negative = skip). */
+int b200_qknorm_rotary_append(void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v, int64_t v_stride,
+                              const void* q_norm, const void* k_norm, float eps, const double* freqs, int rot_dims,
+                              int interleaved, void* k_pool, void* v_pool, const int64_t* slot_mapping,
+                              const int32_t* tok_pos, int n_tok, int H, int G, int dk, int dv, int block_size,
+                              int64_t max_blocks, int dtype, void* stream);
+
+/* Retention per (sequence, head) over the sequence's tokens of this step, in order (SeqSpan rows as above):
+ *   S <- decay[h] S + (k_scale k_t) v_t^T;   o_t = S^T q_t
+ * q, k T [n, H*dk] and v T [n, H*dv] are column slices of one tensor (row stride in_stride); decay fp32 [H]; state fp32
+ * [slots, H, dk, dv], read unless the sequence is fresh and written back; o_raw fp32 [n, H, dv].  dk <= 256. */
+int b200_retention_scan(float* o_raw, const void* q, const void* k, const void* v, int64_t in_stride, const float* decay,
+                        float k_scale, float* state, const int32_t* seqs, int n_seqs, int H, int dk, int dv, int dtype,
+                        void* stream);
+
+/* out[n, h*dv + i] = x[n][h][i] * rsqrt(mean_i x^2 + eps) * weight[i] * act(gate[n, h*dv + i]) * out_scale; weight and
+ * gate may be NULL; gate_act 0: sigmoid, 1: SiLU.  x fp32 [n, H, dv]; out T with row stride out_stride. */
+int b200_head_norm_act_gate(void* out, int64_t out_stride, const float* x, const void* weight, const void* gate,
+                            int64_t gate_stride, int gate_act, float out_scale, float eps, int64_t n_tok, int H, int dv,
+                            int dtype, void* stream);
+
+/* y = sa a + sb b (b may be NULL);  x += layer_scale * w_norm * y * rsqrt(mean(y^2) + eps)  in place on the fp32
+ * residual (layer_scale T [width] may be NULL); x_out (T, may be NULL) receives the new x.  a is fp32 (a_is_f32) or T. */
+int b200_branch_postnorm_residual(float* x, const void* a, int64_t a_stride, int a_is_f32, float sa, const void* b,
+                                  int64_t b_stride, float sb, const void* w_norm, const void* layer_scale, void* x_out,
+                                  float eps, int rows, int width, int dtype, void* stream);
+
+/* out[i] = T(x[i]) for n fp32 numbers. */
+int b200_cast_rows(void* out, const float* x, int64_t n, int dtype, void* stream);
+
+/* Routing with softmax scores s over E router outputs: choice scores c = s + correction (NULL: c = s); the experts form
+ * `groups` equal groups of neighbours, only the `keep` groups with the largest best c can be chosen; the `top` largest c
+ * among them are chosen (ties: lowest index); weights = their s over the sum of their s (+ 1e-20). */
+int b200_softmax_group_topk(int32_t* ids, float* weights, const float* logits, const float* correction, int n_tok, int E,
+                            int top, int groups, int keep, void* stream);
+
+/* xs[r] = h[src[r] / top]: the expert-sorted rows, unscaled. */
+int b200_gather_rows(void* xs, const void* h, const int64_t* src, int64_t n_rows, int top, int width, int dtype,
+                     void* stream);
+
+/* out[n] = sum over k (ascending) of weights[n][k] * (ids[n][k] < n_real ? ys[where[n * top + k]] : x_self[n])
+ *          + shared_rows[n] (may be NULL), fp32.  Experts numbered n_real and up return the token's own fp32 row. */
+int b200_weighted_expert_combine(float* out, const void* ys, const int64_t* where, const int32_t* ids, const float* weights,
+                                 const float* x_self, const void* shared_rows, int64_t n_tok, int top, int n_real,
+                                 int width, int dtype, void* stream);
 
 #ifdef __cplusplus
 }
