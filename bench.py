@@ -679,16 +679,22 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="multi-GPU: skip the token checks of the run")
     ap.add_argument("--no-vocab-parallel-head", action="store_true",
                     help="multi-GPU: keep lm_head + argmax on the last stage (instead of the vocabulary-parallel head)")
-    ap.add_argument("--compare", default="", choices=["", "petipel", "sanesun"],
+    ap.add_argument("--compare", default="", choices=["", "petipel", "sanesun", "fibirax"],
                     help="petipel: prompt-pass and decode throughput of the Petipel model class (ragged step engine) beside "
                          "a Llama shape of equal size, with per-kernel times; sanesun: the Sanesun model class beside a "
-                         "Petipel model of equal size; each prints its own JSON line")
+                         "Petipel model of equal size; fibirax: the Fibirax model class beside a Petipel model of equal size; "
+                         "each prints its own JSON line")
     ap.add_argument("--compare-sizes", default="", help="with --compare: comma-separated subset of w1024,w2048,w4096")
     args = ap.parse_args()
     if args.compare == "petipel":
         from dgi_b200.bench_ragged import run as run_compare
 
         run_compare(args, measured_peaks, ClockSampler)
+        return
+    if args.compare == "fibirax":
+        from dgi_b200.bench_ragged import run_fibirax
+
+        run_fibirax(args, measured_peaks, ClockSampler)
         return
     if args.compare == "sanesun":
         from dgi_b200.bench_ragged import run_sanesun

@@ -9,6 +9,10 @@ so per size.  One JSON line on stdout; the default workload and output line of b
 ``bench.py --compare sanesun``: the same two steps for the Sanesun model class beside a Petipel model of equal width,
 depth, head layout and feed-forward size (its closest relative here: attention layers alternating with a recurrence
 on the same engine), with every kernel of both against its floor so that like kernels can be read side by side.
+
+``bench.py --compare fibirax``: the same two steps for the Fibirax model class (a windowed attention AND a retention in
+every layer, routed experts in every layer) beside a Petipel model of equal width, depth, head layout and expert sizes
+whose layers alternate attention and recurrence, again with every kernel of both against its floor.
 """
 from __future__ import annotations
 
@@ -326,6 +330,135 @@ def _sanesun_kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx, hbm, tf) -> D
             "causal_conv_silu": (n_tok * C * 4, 0),
             "delta_scan": (n_tok * RH * (3 * rdk + rdv) * 2 + n_tok * RH * rdv * 4 + 2 * n_seq * RH * rdk * rdv * 4, 0),
             "head_rmsnorm_gated": (n_tok * RH * rdv * 8, 0),
+        }
+        for name, ts in by.items():
+            t = statistics.mean(ts)
+            entry = {"us": round(t * 1e6, 1), "calls": len(ts)}
+            if name in floors:
+                nbytes, flops = floors[name]
+                floor = max(nbytes / hbm, flops / tf)
+                entry["of_floor"] = round(floor / t, 3)
+                entry["bound"] = "math" if flops / tf > nbytes / hbm else "memory"
+            out.setdefault(phase, {})[name] = entry
+    return out
+
+
+# ---- Fibirax beside Petipel ------------------------------------------------------------------------------------------
+FIBIRAX_WINDOW = 512
+
+
+def fibirax_config(s: Dict[str, int]) -> Dict[str, Any]:
+    left = {"heads": s["heads"], "kv_heads": s["kv"], "dim": s["dk"], "vdim": s["dv"], "scale": 1.0 / math.sqrt(s["dk"]),
+            "softcap": 30.0, "mask": {"size": FIBIRAX_WINDOW},
+            "rot": {"base": 10000.0, "dims": s["dk"] // 2,
+                    "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    right = {"heads": s["rheads"], "dim": s["rdk"], "vdim": s["rdv"],
+             "decay": [1.0 - 2.0 ** (-5 - (i % 8)) for i in range(s["rheads"])]}
+    mlp = {"kind": "moe", "expert": {"ff": s["eff"], "limit": 7.0}, "shared": {"ff": s["eff"], "limit": 7.0},
+           "router": {"experts": s["experts"], "identity": 2, "top": s["top"], "groups": {"count": 2, "keep": 1}}}
+    layer = {"type": "parallel", "mixer": {"left": left, "right": right, "left_scale": 0.8, "right_scale": 0.5}, "mlp": mlp}
+    return {"architecture": "Fibirax", "width": s["width"], "vocab": VOCAB, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "layers": [layer] * LAYERS}
+
+
+def petipel_moe_config(s: Dict[str, int]) -> Dict[str, Any]:
+    raw = petipel_config(s)
+    for layer in raw["layers"]:
+        layer["mlp"] = {"kind": "moe", "expert": {"ff": s["eff"], "limit": 7.0},
+                        "router": {"experts": s["experts"], "top": s["top"]}}
+    return raw
+
+
+def run_fibirax(args, measured_peaks, ClockSampler) -> None:
+    from . import fibirax_layer as Fx
+    from . import mixer_ops
+    from . import petipel_layer as P
+    from .ragged_engine import RaggedStepEngine
+
+    dev = "cuda:0"
+    peaks, how = measured_peaks()
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    steps, warmup = max(3, args.steps), max(3, args.warmup)
+    B, Pn, ctx, Bd = 8, 2048, 2048, 64
+    g = torch.Generator().manual_seed(0)
+    sampler = ClockSampler(0)
+    sampler.start()
+    report: Dict[str, Any] = {}
+    for name, s in SIZES.items():
+        if args.compare_sizes and name not in args.compare_sizes.split(","):
+            continue
+        row: Dict[str, Any] = {}
+        prompts = torch.randint(0, VOCAB, (Bd, ctx), generator=g).tolist()
+        for label, mod, raw in (("fibirax", Fx, fibirax_config(s)), ("petipel", P, petipel_moe_config(s))):
+            cfg = (Fx.FibiraxConfig if mod is Fx else P.PetipelConfig).from_dict(raw)
+            shards = mod.build_shards(cfg, mod.random_checkpoint(cfg, seed=0), [(0, LAYERS)], dev, torch.bfloat16)
+            eng = RaggedStepEngine(shards, max_tokens=Bd * (ctx + 64), max_seqs=Bd, fp32_logits=False)
+
+            def prompt_step():
+                eng.step([(i, prompts[i][:Pn], [Pn - 1]) for i in range(B)])
+                for i in range(B):
+                    eng.finish(i)
+
+            ms = _time_steps(prompt_step, steps, warmup)
+            row[label + "_prefill_tok_s"] = round(B * Pn / ms * 1e3)
+            mixer_ops.EVENTS = []
+            prompt_step()
+            torch.cuda.synchronize()
+            ev_prompt, mixer_ops.EVENTS = mixer_ops.EVENTS, None
+            for i in range(0, Bd, B):
+                eng.step([(j, prompts[j], []) for j in range(i, i + B)])
+            nxt = [[1] for _ in range(Bd)]
+
+            def decode_step():
+                eng.step([(j, nxt[j], [0]) for j in range(Bd)])
+
+            n_dec = min(steps, 32)
+            ms = _time_steps(decode_step, n_dec, warmup)
+            row[label + "_decode_tok_s"] = round(Bd / ms * 1e3)
+            mixer_ops.EVENTS = []
+            decode_step()
+            torch.cuda.synchronize()
+            ev_decode, mixer_ops.EVENTS = mixer_ops.EVENTS, None
+            eng.release()
+            table = _kernel_table if mod is P else _fibirax_kernel_table
+            row[label + "_kernels"] = table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx + warmup + n_dec, hbm, tf)
+            del eng, shards
+            torch.cuda.empty_cache()
+        row["inputs_exceed_l2"] = bool(Bd * ctx * s["kv"] * (s["dk"] + s["dv"]) * 2 > 126e6)
+        report[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"bench": "fibirax_vs_petipel", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+                      "layers": LAYERS, "prompt_step": f"{B} x {Pn} tokens", "decode_step": f"{Bd} sequences at {ctx}",
+                      "peaks": how, "sizes": report, "clocks": clocks}), flush=True)
+
+
+def _fibirax_kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx, hbm, tf) -> Dict[str, Any]:
+    """Like ``_kernel_table`` for the Fibirax kernels (the clamped GLU runs for the routed and for the shared expert:
+    its floor is stated for the mean of the two)."""
+    out: Dict[str, Any] = {}
+    W, H, G, dk, dv = s["width"], s["heads"], s["kv"], s["dk"], s["dv"]
+    RH, rdk, rdv, top = s["rheads"], s["rdk"], s["rdv"], s["top"]
+    for phase, events, n_tok, past in (("prompt", ev_prompt, B * Pn, 0), ("decode", ev_decode, Bd, ctx)):
+        by: Dict[str, List[float]] = {}
+        for name, a, b in events:
+            by.setdefault(name, []).append(a.elapsed_time(b) * 1e-3)
+        per_seq = n_tok // (B if phase == "prompt" else Bd)
+        n_seq = n_tok // per_seq
+        pairs_win = sum(min(past + t + 1, FIBIRAX_WINDOW) for t in range(per_seq))
+        keys_win = min(past + per_seq, FIBIRAX_WINDOW + per_seq)
+        attn = (n_seq * keys_win * G * (dk + dv) * 2 + n_tok * H * (dk + dv) * 2, n_seq * H * 2 * (dk + dv) * pairs_win)
+        floors = {
+            "cast_rows": (n_tok * W * 6, 0),
+            "rms_norm": (n_tok * W * 6, 0),
+            "branch_postnorm_residual": (n_tok * W * (4 + 4 + 2 + 2), 0),
+            "qknorm_rotary_append": (n_tok * (H * dk * 2 + G * (dk + dv) * 2) * 2, 0),
+            "mixed_prompt_attention": attn,
+            "mixed_paged_attention": attn,
+            "retention_scan": (n_tok * RH * (2 * rdk + rdv) * 2 + n_tok * RH * rdv * 4 + 2 * n_seq * RH * rdk * rdv * 4, 0),
+            "head_norm_act_gate": (n_tok * RH * rdv * 8, 0),
+            "clamped_glu": (n_tok * (top + 1) // 2 * s["eff"] * 6, 0),
+            "gather_rows": (n_tok * top * W * 4, 0),
+            "weighted_expert_combine": (n_tok * top * W * 2 + n_tok * W * (4 + 4 + 2), 0),
         }
         for name, ts in by.items():
             t = statistics.mean(ts)

@@ -493,6 +493,12 @@ __device__ __forceinline__ void stage16(void* smem_dst, const void* gmem_src, bo
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(bytes) : "memory");
 }
 
+// c * tanh(s / c) as c * (1 - 2 / (exp(2 s / c) + 1)) with the hardware exponential and reciprocal: absolute error of a
+// few 1e-7 * c, far below the rounding of the 16-bit weights the scores turn into (two_over_c = 2 / c)
+__device__ __forceinline__ float soft_cap(float s, float c, float two_over_c) {
+  return c * (1.0f - __fdividef(2.0f, __expf(s * two_over_c) + 1.0f));
+}
+
 constexpr int kTcWarps = 8;
 constexpr int kTcKeys = 32;
 constexpr int kTcRows = 16;
@@ -549,6 +555,7 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
     for (int nt = 0; nt < DV8; ++nt) O[hw][nt][0] = O[hw][nt][1] = O[hw][nt][2] = O[hw][nt][3] = 0.f;
   }
   const T* qbase = static_cast<const T*>(A.q);
+  const float cap2 = A.softcap > 0.f ? 2.0f / A.softcap : 0.f;
   // S fragments of one head against the staged K tile; rows past the tile's tokens read zeros
   auto scores = [&](int h, float (&s)[4][4]) {
 #pragma unroll
@@ -663,7 +670,7 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
           for (int e = 0; e < 2; ++e) {
             const int j = j0 + nt * 8 + qc + e;
             const bool ok = row_ok && j <= p && (A.window <= 0 || p - j < A.window || j < A.keep_first);
-            if (A.softcap > 0.f) s[nt][2 * half + e] = A.softcap * tanhf(s[nt][2 * half + e] / A.softcap);
+            if (A.softcap > 0.f) s[nt][2 * half + e] = soft_cap(s[nt][2 * half + e], A.softcap, cap2);
             if (!ok) s[nt][2 * half + e] = -INFINITY;
             mx = fmaxf(mx, s[nt][2 * half + e]);
           }
@@ -874,7 +881,10 @@ struct TcPlan {
 inline bool tc_plan(int H, int G, int dk, int dv, bool has_talk, bool same_pool, bool unrotate, int dtype, TcPlan* plan) {
   if (dtype == B200_DTYPE_F32 || dk % 16 || dv % 8 || dv > 256 || H % G) return false;
   const int dv8 = dv <= 64 ? 8 : (dv <= 128 ? 16 : 32), dvp = dv8 * 8;
-  const int hw = (dv8 <= 16 && H > kTcWarps) ? 2 : 1;
+  // two heads per warp pay when the CTA's heads share what is staged: with a mixing matrix (all heads' raw scores are
+  // formed anyway) or when one kv head serves more heads than a CTA has warps; plain grouped-query layouts run one
+  // head per warp, which halves the staged kv heads per CTA and lets two CTAs share an SM
+  const int hw = (dv8 <= 16 && H > kTcWarps && (has_talk || H / G > kTcWarps)) ? 2 : 1;
   const int gs = has_talk ? G : std::min(G, (kTcWarps * hw + H / G - 1) / (H / G) + 1);
   const bool alias = same_pool && dk == dvp;
   size_t stage = static_cast<size_t>(gs) * kTcKeys * (dk + 8) * 2;
