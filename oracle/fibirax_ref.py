@@ -51,54 +51,69 @@ def rotate_pairs(x: torch.Tensor, pos: torch.Tensor, freqs: torch.Tensor) -> tor
     return out
 
 
-def window_sink_attention(h: torch.Tensor, spec: dict, t: Dict[str, torch.Tensor], eps: float) -> torch.Tensor:
-    """Grouped-query attention; q / k are RMS-normed per head, partly rotated; scores are scaled, soft-capped by
-    c * tanh(s / c), limited to the last ``mask.size`` positions, and normalised with 1 + sum exp in the denominator."""
-    T = h.shape[0]
-    H, G, dk, dv = int(spec["heads"]), int(spec["kv_heads"]), int(spec["dim"]), int(spec["vdim"])
-    q = (h @ t["q"].T).view(T, H, dk)
-    k = (h @ t["k"].T).view(T, G, dk)
-    v = (h @ t["v"].T).view(T, G, dv)
-    q, k = rms(q, eps, t["q.norm"]), rms(k, eps, t["k.norm"])
-    rot = spec.get("rot")
+def capped_window_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float, window: int = 0,
+                            cap: float = 0.0, sink: bool = True) -> torch.Tensor:
+    """q ``[T, H, dk]``, k ``[T, G, dk]``, v ``[T, G, dv]`` of one sequence -> ``[T, H, dv]``.  Scores are scaled, bounded
+    by cap * tanh(s / cap), limited to the last ``window`` positions, and normalised with 1 + sum exp (``sink``)."""
+    T, H, _ = q.shape
+    rep = H // k.shape[1]
     pos = torch.arange(T)
-    if rot and int(rot.get("dims", 0)) > 0:
-        f = rotary_frequencies(int(rot["dims"]), float(rot["base"]), rot.get("scaling"), dtype=h.dtype)
-        q, k = rotate_pairs(q, pos, f), rotate_pairs(k, pos, f)
-    rep = H // G
-    out = torch.zeros(T, H, dv, dtype=h.dtype)
-    cap = float(spec.get("softcap") or 0.0)
-    win = int((spec.get("mask") or {}).get("size", 0))
     dist = pos[:, None] - pos[None, :]
-    seen = (dist >= 0) & ((dist < win) if win > 0 else torch.ones_like(dist, dtype=torch.bool))
+    seen = (dist >= 0) & ((dist < window) if window > 0 else torch.ones_like(dist, dtype=torch.bool))
+    out = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
     for hd in range(H):
-        s = (q[:, hd] @ k[:, hd // rep].T) * float(spec["scale"])
+        s = (q[:, hd] @ k[:, hd // rep].T) * scale
         if cap > 0:
             s = cap * torch.tanh(s / cap)
         e = torch.where(seen, torch.exp(s), torch.zeros_like(s))
-        p = e / (1.0 + e.sum(dim=1, keepdim=True))
-        out[:, hd] = p @ v[:, hd // rep]
+        out[:, hd] = (e / ((1.0 if sink else 0.0) + e.sum(dim=1, keepdim=True))) @ v[:, hd // rep]
+    return out
+
+
+def window_sink_attention(h: torch.Tensor, spec: dict, t: Dict[str, torch.Tensor], eps: float) -> torch.Tensor:
+    """The left mixer: projections, per-head q / k norm, partial rotation, the attention above, output projection."""
+    T = h.shape[0]
+    H, G, dk, dv = int(spec["heads"]), int(spec.get("kv_heads", spec["heads"])), int(spec["dim"]), int(spec["vdim"])
+    q = (h @ t["q"].T).view(T, H, dk)
+    k = (h @ t["k"].T).view(T, G, dk)
+    v = (h @ t["v"].T).view(T, G, dv)
+    if "q.norm" in t:
+        q = rms(q, eps, t["q.norm"])
+    if "k.norm" in t:
+        k = rms(k, eps, t["k.norm"])
+    rot = spec.get("rot")
+    if rot and int(rot.get("dims", 0)) > 0:
+        f = rotary_frequencies(int(rot["dims"]), float(rot["base"]), rot.get("scaling"), dtype=h.dtype)
+        q, k = rotate_pairs(q, torch.arange(T), f), rotate_pairs(k, torch.arange(T), f)
+    out = capped_window_attention(q, k, v, float(spec["scale"]), int((spec.get("mask") or {}).get("size", 0)),
+                                  float(spec.get("softcap") or 0.0))
     return out.reshape(T, H * dv) @ t["o"].T
 
 
+def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay, state: Optional[torch.Tensor] = None):
+    """q, k ``[T, H, dk]`` (k already scaled), v ``[T, H, dv]``: S_t = d_h S_(t-1) + k_t v_t^T, o_t = S_t^T q_t, token by
+    token.  Returns (o ``[T, H, dv]``, the final state ``[H, dk, dv]``)."""
+    T, H, dk = q.shape
+    S = torch.zeros(H, dk, v.shape[2], dtype=q.dtype) if state is None else state.clone()
+    o = torch.zeros(T, H, v.shape[2], dtype=q.dtype)
+    for n in range(T):
+        for hd in range(H):
+            S[hd] = float(decay[hd]) * S[hd] + torch.outer(k[n, hd], v[n, hd])
+            o[n, hd] = S[hd].T @ q[n, hd]
+    return o, S
+
+
 def retention(h: torch.Tensor, spec: dict, t: Dict[str, torch.Tensor], eps: float) -> torch.Tensor:
-    """S_t = d_h S_(t-1) + k_t v_t^T (k scaled by dk^-1/2), o_t = S_t^T q_t; every head's o is made unit-RMS, gated by
-    silu(W_g h) and projected."""
+    """The right mixer: k scaled by dk^-1/2, the scan above, every head's read-out made unit-RMS, gated by silu(W_g h)
+    and projected."""
     T = h.shape[0]
     H, dk, dv = int(spec["heads"]), int(spec["dim"]), int(spec["vdim"])
     q = (h @ t["q"].T).view(T, H, dk)
     k = (h @ t["k"].T).view(T, H, dk) * dk ** -0.5
     v = (h @ t["v"].T).view(T, H, dv)
-    o = torch.zeros(T, H, dv, dtype=h.dtype)
-    for hd in range(H):
-        S = torch.zeros(dk, dv, dtype=h.dtype)
-        d = float(spec["decay"][hd])
-        for n in range(T):
-            S = d * S + torch.outer(k[n, hd], v[n, hd])
-            o[n, hd] = S.T @ q[n, hd]
+    o, _ = retention_scan(q, k, v, spec["decay"])
     g = h @ t["g"].T
-    y = rms(o, eps).reshape(T, H * dv) * (g * torch.sigmoid(g))
-    return y @ t["o"].T
+    return (rms(o, eps).reshape(T, H * dv) * (g * torch.sigmoid(g))) @ t["o"].T
 
 
 def clamped_expert(h: torch.Tensor, t: Dict[str, torch.Tensor], pre: str, limit: float) -> torch.Tensor:
@@ -129,7 +144,8 @@ def routed_ff(h: torch.Tensor, spec: dict, t: Dict[str, torch.Tensor]) -> torch.
     E, ident, top = int(r["experts"]), int(r.get("identity", 0)), int(r["top"])
     grp = r.get("groups") or {}
     corr = t["correction"].to(h.dtype) if "correction" in t else torch.zeros(E + ident, dtype=h.dtype)
-    ids, w = route(h @ t["router"].to(h.dtype).T, corr, top, int(grp.get("count", 1)), int(grp.get("keep", 1)))
+    ids, w = route(h @ t["router"].to(h.dtype).T, corr, top, int(grp.get("count", 1)),
+                   int(grp.get("keep", grp.get("count", 1))))
     out = torch.zeros_like(h)
     limit = float(spec["expert"]["limit"])
     for n in range(h.shape[0]):
@@ -166,3 +182,12 @@ def forward(config: dict, tensors: Dict[str, torch.Tensor], tokens: List[int], d
         if layers_out is not None:
             layers_out.append(x.clone())
     return rms(x, eps, t["final.norm"]) @ t["head"].T
+
+
+def greedy(config: dict, tensors: Dict[str, torch.Tensor], prompt: List[int], n_new: int) -> List[int]:
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        nxt = int(forward(config, tensors, toks)[-1].argmax())
+        out.append(nxt)
+        toks.append(nxt)
+    return out
