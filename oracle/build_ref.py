@@ -37,6 +37,12 @@ MODULES = {
 }
 
 
+def sources_present(ref_root: str = REF_ROOT) -> bool:
+    """True where the reference's sources of every listed module lie under ``ref_root`` (a mounted but empty folder
+    does not count)."""
+    return all(os.path.isfile(os.path.join(ref_root, rel)) for rel in MODULES.values())
+
+
 def build(ref_root: str = REF_ROOT, out_dir: str = OUT_DIR) -> list:
     """Compile every module of MODULES; returns the files written.  Raises if a source is missing or does not compile."""
     os.makedirs(out_dir, exist_ok=True)

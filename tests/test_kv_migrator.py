@@ -49,7 +49,7 @@ def _reference_pd_scheduler():
 
     from oracle import build_ref, ref_loader
 
-    if not os.path.exists(ref_loader.path_of("pd_scheduler")) and os.path.isdir(build_ref.REF_ROOT):
+    if not os.path.exists(ref_loader.path_of("pd_scheduler")) and build_ref.sources_present():
         build_ref.build()
     module = ref_loader.load("pd_scheduler")
     if module is None:

@@ -17,7 +17,7 @@ from oracle import build_ref, host_logic as H, llama_ref as L, ref_loader
 
 @pytest.fixture(scope="module")
 def ref():
-    if not os.path.exists(ref_loader.path_of("model_shard")) and os.path.isdir(build_ref.REF_ROOT):
+    if not os.path.exists(ref_loader.path_of("model_shard")) and build_ref.sources_present():
         build_ref.build()
     mods = {name: ref_loader.load(name) for name in build_ref.MODULES}
     if any(m is None for m in mods.values()):

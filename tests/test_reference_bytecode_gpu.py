@@ -19,7 +19,7 @@ DEV = "cuda:0"
 
 @pytest.fixture(scope="module")
 def ref():
-    if not os.path.exists(ref_loader.path_of("kv_cache")) and os.path.isdir(build_ref.REF_ROOT):
+    if not os.path.exists(ref_loader.path_of("kv_cache")) and build_ref.sources_present():
         build_ref.build()
     mods = {name: ref_loader.load(name) for name in build_ref.MODULES}
     if any(m is None for m in mods.values()):
