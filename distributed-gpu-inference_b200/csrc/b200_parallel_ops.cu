@@ -469,10 +469,10 @@ int b200_retention_scan(float* o_raw, const void* q, const void* k, const void* 
                         float k_scale, float* state, const int32_t* seqs, int n_seqs, int H, int dk, int dv, int dtype,
                         void* stream) {
   if (n_seqs < 0 || H <= 0 || dk <= 0 || dv <= 0) return fail(B200_EINVAL, "b200_retention_scan: bad sizes");
-  if (dk > 256) return fail(B200_ESHAPE, "b200_retention_scan: key size %d beyond 256", dk);
+  if (dk > 512) return fail(B200_ESHAPE, "b200_retention_scan: key size %d beyond 512", dk);
   if (n_seqs == 0) return 0;
   if (!o_raw || !q || !k || !v || !decay || !state || !seqs) return fail(B200_EINVAL, "b200_retention_scan: null pointer");
-  const int dkt = dk <= 32 ? 32 : (dk <= 64 ? 64 : (dk <= 128 ? 128 : 256));
+  const int dkt = dk <= 32 ? 32 : (dk <= 64 ? 64 : (dk <= 128 ? 128 : (dk <= 256 ? 256 : 512)));
   const size_t smem = sizeof(float) * std::max<size_t>(2 * kRetChunk * (2 * static_cast<size_t>(dkt) + kRetCols),
                                                        static_cast<size_t>(dk) * kRetCols);
   const dim3 grid(n_seqs, H, (dv + kRetCols - 1) / kRetCols);
@@ -487,7 +487,8 @@ int b200_retention_scan(float* o_raw, const void* q, const void* k, const void* 
     if (dkt == 32) launch(retention_scan_kernel<T, 32>);
     else if (dkt == 64) launch(retention_scan_kernel<T, 64>);
     else if (dkt == 128) launch(retention_scan_kernel<T, 128>);
-    else launch(retention_scan_kernel<T, 256>);
+    else if (dkt == 256) launch(retention_scan_kernel<T, 256>);
+    else launch(retention_scan_kernel<T, 512>);
     return check_launch("b200_retention_scan");
   });
 }

@@ -216,7 +216,7 @@ int b200_qknorm_rotary_append(void* q, int64_t q_stride, const void* k, int64_t 
 /* Retention per (sequence, head) over the sequence's tokens of this step, in order (SeqSpan rows as above):
  *   S <- decay[h] S + (k_scale k_t) v_t^T;   o_t = S^T q_t
  * q, k T [n, H*dk] and v T [n, H*dv] are column slices of one tensor (row stride in_stride); decay fp32 [H]; state fp32
- * [slots, H, dk, dv], read unless the sequence is fresh and written back; o_raw fp32 [n, H, dv].  dk <= 256. */
+ * [slots, H, dk, dv], read unless the sequence is fresh and written back; o_raw fp32 [n, H, dv].  dk <= 512. */
 int b200_retention_scan(float* o_raw, const void* q, const void* k, const void* v, int64_t in_stride, const float* decay,
                         float k_scale, float* state, const int32_t* seqs, int n_seqs, int H, int dk, int dv, int dtype,
                         void* stream);

@@ -259,7 +259,7 @@ def test_tensor_core_attention_matches_the_statement(dt, H, G, dk, dv, win):
     close(out2.cpu(), ref, tol)
 
 
-@pytest.mark.parametrize("H,dk,dv", [(3, 12, 20), (1, 40, 33), (2, 130, 8), (2, 64, 64), (1, 256, 5), (1, 2, 2)])
+@pytest.mark.parametrize("H,dk,dv", [(3, 12, 20), (1, 40, 33), (2, 130, 8), (2, 64, 64), (1, 256, 5), (1, 300, 6), (1, 2, 2)])
 def test_retention_state_through_portions_and_slots(H, dk, dv):
     from dgi_b200 import mixer_ops as M
 
