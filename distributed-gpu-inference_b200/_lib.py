@@ -167,6 +167,10 @@ MIXER_SIGNATURES = {
     "b200_retention_scan": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int,
                 c_int, c_int, c_int, c_void_p]),
+    "b200_retention_carry": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200_retention_apply_carry": (
+        c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_head_norm_act_gate": (
         c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_float, c_float, c_int64, c_int, c_int,
                 c_int, c_void_p]),

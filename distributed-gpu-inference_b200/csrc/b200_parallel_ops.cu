@@ -5,7 +5,8 @@
 //   q/k norm + rotary append    per-head weighted RMS norm of q and k, partial rotary with a frequency TABLE (so any
 //                               frequency rescaling is the caller's), k and v scattered into the paged pools
 //   retention scan              S_t = d_h S_(t-1) + (c k_t) v_t^T,  o_t = S_t^T q_t  with a fixed decay per head, the fp32
-//                               state carried per sequence in a slot pool
+//                               state carried per sequence in a slot pool; long portions run as parallel segments
+//                               whose missing carry is added afterwards
 //   head norm with a gate       o * rsqrt(mean(o^2) + eps) [* w] * act(gate) * out_scale, act = sigmoid or SiLU
 //   branch post-norm residual   y = sa a + sb b;  x += ls * w * y * rsqrt(mean(y^2) + eps);  optional copy of x in T
 //   grouped softmax routing     softmax scores, choice by score + bias inside the best expert groups, weights = chosen
@@ -159,21 +160,53 @@ retention_scan_kernel(float* __restrict__ o_raw, const T* __restrict__ q, const 
   }
   __syncthreads();
   constexpr int kPer = (kRetChunk * row_len + kRetNT - 1) / kRetNT;
+  // staged element e = thread + u * 128 of a chunk is (token e / row_len, slot e % row_len); where it comes from does
+  // not change from chunk to chunk, so for key sizes whose tables fit in registers the source pointer, the token and
+  // the factor (k_scale on key slots) of every element are worked out once
+  constexpr bool kTabled = DK <= 128;
+  constexpr int kTab = kTabled ? kPer : 1;
   T raw[kPer];
-  auto fetch = [&](int t0) {
+  const T* src[kTab];
+  int tok_of[kTab];
+  float mul[kTab];
+  if constexpr (kTabled) {
 #pragma unroll
     for (int u = 0; u < kPer; ++u) {
       const int e = threadIdx.x + u * kRetNT;
       const int tt = e / row_len, sl = e - tt * row_len;
-      raw[u] = Cvt<T>::from_f32(0.f);
-      if (tt < kRetChunk && t0 + tt < sq.count) {
-        const int64_t row = static_cast<int64_t>(sq.tok0 + t0 + tt) * in_stride;
+      src[u] = nullptr;
+      tok_of[u] = tt;
+      mul[u] = (sl >= DK && sl < 2 * DK) ? k_scale : 1.0f;
+      if (tt < kRetChunk) {
+        const int64_t row = static_cast<int64_t>(sq.tok0 + tt) * in_stride;
         if (sl < 2 * DK) {
           const int s2 = sl < DK ? sl : sl - DK;
           const int i = 4 * (s2 % RW4) + s2 / RW4;
-          if (i < dk) raw[u] = sl < DK ? q[row + h * dk + i] : k[row + h * dk + i];
+          if (i < dk) src[u] = (sl < DK ? q : k) + row + h * dk + i;
         } else if (sl - 2 * DK < ncol) {
-          raw[u] = v[row + h * dv + col0 + sl - 2 * DK];
+          src[u] = v + row + h * dv + col0 + sl - 2 * DK;
+        }
+      }
+    }
+  }
+  auto fetch = [&](int t0) {
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+      raw[u] = Cvt<T>::from_f32(0.f);
+      if constexpr (kTabled) {
+        if (src[u] != nullptr && t0 + tok_of[u] < sq.count) raw[u] = src[u][static_cast<int64_t>(t0) * in_stride];
+      } else {
+        const int e = threadIdx.x + u * kRetNT;
+        const int tt = e / row_len, sl = e - tt * row_len;
+        if (tt < kRetChunk && t0 + tt < sq.count) {
+          const int64_t row = static_cast<int64_t>(sq.tok0 + t0 + tt) * in_stride;
+          if (sl < 2 * DK) {
+            const int s2 = sl < DK ? sl : sl - DK;
+            const int i = 4 * (s2 % RW4) + s2 / RW4;
+            if (i < dk) raw[u] = sl < DK ? q[row + h * dk + i] : k[row + h * dk + i];
+          } else if (sl - 2 * DK < ncol) {
+            raw[u] = v[row + h * dv + col0 + sl - 2 * DK];
+          }
         }
       }
     }
@@ -182,11 +215,15 @@ retention_scan_kernel(float* __restrict__ o_raw, const T* __restrict__ q, const 
 #pragma unroll
     for (int u = 0; u < kPer; ++u) {
       const int e = threadIdx.x + u * kRetNT;
-      const int tt = e / row_len, sl = e - tt * row_len;
-      if (tt < n_valid) {
-        float val = Cvt<T>::to_f32(raw[u]);
-        if (sl >= DK && sl < 2 * DK) val *= k_scale;
-        dst[e] = val;
+      if constexpr (kTabled) {
+        if (tok_of[u] < n_valid) dst[e] = Cvt<T>::to_f32(raw[u]) * mul[u];
+      } else {
+        const int tt = e / row_len, sl = e - tt * row_len;
+        if (tt < n_valid) {
+          float val = Cvt<T>::to_f32(raw[u]);
+          if (sl >= DK && sl < 2 * DK) val *= k_scale;
+          dst[e] = val;
+        }
       }
     }
   };
@@ -235,6 +272,91 @@ retention_scan_kernel(float* __restrict__ o_raw, const T* __restrict__ q, const 
   for (int idx = threadIdx.x; idx < dk * kRetCols; idx += kRetNT) {
     const int i = idx / kRetCols, c = idx - i * kRetCols;
     if (c < ncol) st[i * dv + col0 + c] = ret_sm[idx];
+  }
+}
+
+// ---- retention over long portions: segments in parallel, then the carry ---------------------------------------------
+// A long portion is cut into segments that the scan above runs as independent fresh sequences (their end states go to a
+// scratch tensor, one slot per segment).  The decay is a constant per head, so what a segment misses is exactly
+//   o_t += d^(t - t0 + 1) P^T q_t        with P the true state at the segment's start,
+// and P follows from the segments' end states E_j by  P_(j+1) = d^(n_j) P_j + E_j.
+// retention_carry: one thread per state element walks a parent's segments, leaves P_j where E_j was and the parent's
+// final state in its slot.  parents rows: (first segment, segments, state slot, fresh).
+__global__ void __launch_bounds__(256)
+retention_carry_kernel(float* __restrict__ state, float* __restrict__ seg_state, const int32_t* __restrict__ parents,
+                       const RetSeq* __restrict__ segs, const float* __restrict__ decay, int H, int64_t per_head) {
+  const int32_t* pr = parents + 4 * blockIdx.x;
+  const int h = blockIdx.y;
+  const int64_t e = static_cast<int64_t>(blockIdx.z) * blockDim.x + threadIdx.x;
+  if (e >= per_head) return;
+  const float d = decay[h];
+  float* st = state + (static_cast<int64_t>(pr[2]) * H + h) * per_head + e;
+  float P = pr[3] ? 0.f : *st;
+  for (int j = 0; j < pr[1]; ++j) {
+    float* sp = seg_state + (static_cast<int64_t>(pr[0] + j) * H + h) * per_head + e;
+    const float E = *sp;
+    *sp = P;
+    P = fmaf(powf(d, static_cast<float>(segs[pr[0] + j].count)), P, E);
+  }
+  *st = P;
+}
+
+// retention_apply_carry: one CTA (128 threads) per (segment, head, 32 value columns); the start state's slab sits in
+// shared memory, the segment's q rows pass through it 16 tokens at a time; warp w owns tokens 4w .. 4w + 3 of a tile,
+// lane c one column.
+constexpr int kCarryTok = 16;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+retention_apply_carry_kernel(float* __restrict__ o_raw, const T* __restrict__ q, int64_t in_stride,
+                             const float* __restrict__ seg_state, const RetSeq* __restrict__ segs,
+                             const float* __restrict__ decay, int H, int dk, int dv) {
+  extern __shared__ __align__(16) float ca_sm[];
+  const RetSeq sg = segs[blockIdx.x];
+  const int h = blockIdx.y, col0 = blockIdx.z * 32;
+  const int warp = threadIdx.x >> 5, cl = threadIdx.x & 31;
+  const int dkp = (dk + 3) & ~3;
+  float* P_s = ca_sm;                 // [dkp][32]
+  float* q_s = P_s + dkp * 32;        // [kCarryTok][dkp]
+  const float* P = seg_state + (static_cast<int64_t>(blockIdx.x) * H + h) * dk * dv;
+  for (int idx = threadIdx.x; idx < dkp * 32; idx += blockDim.x) {
+    const int i = idx >> 5, c = idx & 31;
+    P_s[idx] = (i < dk && col0 + c < dv) ? P[i * dv + col0 + c] : 0.f;
+  }
+  const float d = decay[h];
+  const float d_tile = powf(d, static_cast<float>(kCarryTok));
+  float f[4];
+#pragma unroll
+  for (int jj = 0; jj < 4; ++jj) f[jj] = powf(d, static_cast<float>(warp * 4 + jj + 1));
+  for (int t0 = 0; t0 < sg.count; t0 += kCarryTok) {
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < kCarryTok * dkp; idx += blockDim.x) {
+      const int t = idx / dkp, i = idx - t * dkp;
+      q_s[idx] = (t0 + t < sg.count && i < dk)
+                     ? Cvt<T>::to_f32(q[static_cast<int64_t>(sg.tok0 + t0 + t) * in_stride + h * dk + i]) : 0.f;
+    }
+    __syncthreads();
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int i = 0; i < dkp; i += 4) {
+      const float p0 = P_s[i * 32 + cl], p1 = P_s[(i + 1) * 32 + cl], p2 = P_s[(i + 2) * 32 + cl], p3 = P_s[(i + 3) * 32 + cl];
+#pragma unroll
+      for (int jj = 0; jj < 4; ++jj) {
+        const float4 q4 = *reinterpret_cast<const float4*>(q_s + (warp * 4 + jj) * dkp + i);
+        acc[jj] = fmaf(p0, q4.x, acc[jj]);
+        acc[jj] = fmaf(p1, q4.y, acc[jj]);
+        acc[jj] = fmaf(p2, q4.z, acc[jj]);
+        acc[jj] = fmaf(p3, q4.w, acc[jj]);
+      }
+    }
+#pragma unroll
+    for (int jj = 0; jj < 4; ++jj) {
+      const int t = t0 + warp * 4 + jj;
+      if (t < sg.count && col0 + cl < dv) {
+        float* o = o_raw + (static_cast<int64_t>(sg.tok0 + t) * H + h) * dv + col0 + cl;
+        *o = fmaf(f[jj], acc[jj], *o);
+      }
+      f[jj] *= d_tile;
+    }
   }
 }
 
@@ -490,6 +612,38 @@ int b200_retention_scan(float* o_raw, const void* q, const void* k, const void* 
     else if (dkt == 256) launch(retention_scan_kernel<T, 256>);
     else launch(retention_scan_kernel<T, 512>);
     return check_launch("b200_retention_scan");
+  });
+}
+
+int b200_retention_carry(float* state, float* seg_state, const int32_t* parents, int n_parents, const int32_t* seg_spans,
+                         const float* decay, int H, int dk, int dv, void* stream) {
+  if (n_parents < 0 || H <= 0 || dk <= 0 || dv <= 0) return fail(B200_EINVAL, "b200_retention_carry: bad sizes");
+  if (n_parents == 0) return 0;
+  if (!state || !seg_state || !parents || !seg_spans || !decay) return fail(B200_EINVAL, "b200_retention_carry: null pointer");
+  const int64_t per_head = static_cast<int64_t>(dk) * dv;
+  const dim3 grid(n_parents, H, static_cast<unsigned>((per_head + 255) / 256));
+  retention_carry_kernel<<<grid, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      state, seg_state, parents, reinterpret_cast<const RetSeq*>(seg_spans), decay, H, per_head);
+  return check_launch("b200_retention_carry");
+}
+
+int b200_retention_apply_carry(float* o_raw, const void* q, int64_t in_stride, const float* seg_state,
+                               const int32_t* seg_spans, int n_segs, const float* decay, int H, int dk, int dv, int dtype,
+                               void* stream) {
+  if (n_segs < 0 || H <= 0 || dk <= 0 || dv <= 0) return fail(B200_EINVAL, "b200_retention_apply_carry: bad sizes");
+  if (n_segs == 0) return 0;
+  if (!o_raw || !q || !seg_state || !seg_spans || !decay) return fail(B200_EINVAL, "b200_retention_apply_carry: null pointer");
+  const int dkp = (dk + 3) & ~3;
+  const size_t smem = sizeof(float) * static_cast<size_t>(dkp) * (32 + kCarryTok);
+  if (smem > 200 * 1024) return fail(B200_ESHAPE, "b200_retention_apply_carry: key size %d too large", dk);
+  const dim3 grid(n_segs, H, (dv + 31) / 32);
+  return parallel_by_dtype(dtype, "b200_retention_apply_carry", [&](auto* tag) {
+    using T = std::remove_pointer_t<decltype(tag)>;
+    auto kern = retention_apply_carry_kernel<T>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+    kern<<<grid, 128, smem, static_cast<cudaStream_t>(stream)>>>(o_raw, static_cast<const T*>(q), in_stride, seg_state,
+                                                                 reinterpret_cast<const RetSeq*>(seg_spans), decay, H, dk, dv);
+    return check_launch("b200_retention_apply_carry");
   });
 }
 

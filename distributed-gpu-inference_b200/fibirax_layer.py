@@ -187,7 +187,8 @@ class ParallelMixer(nn.Module):
                                             softcap=self.softcap)
         # right: retention over the state slots
         o = mixer_ops.retention_scan(proj[:, c[3]:c[3] + Hr * dkr], proj[:, c[4]:c[4] + Hr * dkr],
-                                     proj[:, c[5]:c[5] + Hr * dvr], self.decay, dkr ** -0.5, cache.rstate, st.scan_seqs)
+                                     proj[:, c[5]:c[5] + Hr * dvr], self.decay, dkr ** -0.5, cache.rstate, st.scan_seqs,
+                                     plan=st.scan_plan())
         mixer_ops.head_norm_act_gate(o, None, proj[:, c[6]:c[6] + Hr * dvr], self.eps, h.dtype, gate_act="silu",
                                      out_scale=self.right_gain, out=buf[:, self.Kl:self.Kl + self.Kr])
         return F.linear(buf, self.w_out)
@@ -195,8 +196,9 @@ class ParallelMixer(nn.Module):
 
 class GroupedSoftmaxMoE(nn.Module):
     """Routed experts weighted on the way OUT, identity experts, a shared expert; see the module docstring.  The router
-    reads the fp32 residual; tokens are sorted by expert and pushed through the experts' clamped GLUs (one grouped launch
-    each way for steps of few rows, one vendor GEMM per expert otherwise)."""
+    reads the fp32 residual; tokens are sorted by expert and pushed through the experts' clamped GLUs: one grouped launch
+    each way (this library's kernel for steps of few rows, the vendor's grouped GEMM for long prompt steps, both with
+    the experts' row offsets read on the device), or one vendor GEMM per expert in fp32."""
 
     GROUPED_MAX_ROWS = 2048
 
@@ -218,6 +220,7 @@ class GroupedSoftmaxMoE(nn.Module):
             self.w_down = _param(torch.stack([t[f"e{e}.down"] for e in range(self.E)]), device, dtype)  # [E, W, ff]
         self.grouped = bool(self.E) and (mixer_ops.grouped_linear_supported(self.w_gu.shape[2], self.w_gu.dtype)
                                          and mixer_ops.grouped_linear_supported(self.w_down.shape[2], self.w_down.dtype))
+        self._ar: Optional[torch.Tensor] = None
         self.shared_limit = 0.0
         self.ws_gu = self.ws_down = None
         if spec.get("shared"):
@@ -225,39 +228,48 @@ class GroupedSoftmaxMoE(nn.Module):
             self.ws_gu = _param(torch.cat([t["shared.gate"], t["shared.up"]], dim=0), device, dtype)
             self.ws_down = _param(t["shared.down"], device, dtype)
 
+    def _arange(self, n: int, device) -> torch.Tensor:
+        """``arange(n)`` on the device, cut from a cached longer one."""
+        if self._ar is None or self._ar.numel() < n or self._ar.device != device:
+            self._ar = torch.arange(max(n, 4096), device=device)
+        return self._ar[:n]
+
     def forward(self, h: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         """``h``: the sublayer's input in the experts' dtype, ``x``: the same rows in fp32 (the residual)."""
         n, top, E = h.shape[0], self.top, self.E
         ids, w = mixer_ops.softmax_group_topk(F.linear(x, self.w_router), self.correction, top, self.groups, self.keep)
-        flat = ids.reshape(-1).to(torch.int64)
-        order = torch.argsort(flat, stable=True)
-        counts = torch.bincount(flat, minlength=E + self.ident)
+        # rows in expert order; where each expert's rows start comes from the sorted ids themselves (a search, not a
+        # count: no value ever travels to the host)
+        sorted_ids, order = torch.sort(ids.reshape(-1).to(torch.int64), stable=True)
         where = torch.empty_like(order)
-        where[order] = torch.arange(n * top, device=h.device)
+        where[order] = self._arange(n * top, h.device)
         ys = h.new_empty((0, h.shape[1]))
         if E:
+            offsets = torch.searchsorted(sorted_ids, self._arange(E + 1, h.device)).to(torch.int32)
             xs = mixer_ops.gather_rows(h, order, top)      # identity rows ride at the end and are never multiplied
             if self.grouped and n * top <= self.GROUPED_MAX_ROWS:
-                offsets = torch.zeros(E + 1, dtype=torch.int32, device=h.device)
-                offsets[1:] = torch.cumsum(counts[:E], 0)
                 y = mixer_ops.clamped_glu(mixer_ops.grouped_linear(xs, self.w_gu, offsets), self.limit, GLU_ALPHA)
                 ys = mixer_ops.grouped_linear(y, self.w_down, offsets)
+            elif self.grouped and hasattr(torch, "_grouped_mm"):
+                # long prompt steps: the vendor's grouped GEMM, which also reads the offsets on the device
+                ends = offsets[1:]
+                y = mixer_ops.clamped_glu(torch._grouped_mm(xs, self.w_gu.transpose(1, 2), offs=ends), self.limit, GLU_ALPHA)
+                ys = torch._grouped_mm(y, self.w_down.transpose(1, 2), offs=ends)
             else:
-                host = counts[:E].tolist()
+                # fp32, or sizes off the 16-byte grid: one vendor GEMM per expert; the counts come to the host once
+                bounds = offsets.tolist()
                 gu = torch.empty((n * top, self.w_gu.shape[1]), dtype=h.dtype, device=h.device)
-                lo = 0
-                for e, cnt in enumerate(host):
-                    if cnt:
-                        torch.mm(xs[lo:lo + cnt], self.w_gu[e].t(), out=gu[lo:lo + cnt])
-                        lo += cnt
-                routed = lo
+                for e in range(E):
+                    lo, hi = bounds[e], bounds[e + 1]
+                    if hi > lo:
+                        torch.mm(xs[lo:hi], self.w_gu[e].t(), out=gu[lo:hi])
+                routed = bounds[E]
                 y = mixer_ops.clamped_glu(gu[:routed], self.limit, GLU_ALPHA) if routed else gu[:0, :gu.shape[1] // 2]
                 ys = torch.empty((n * top, h.shape[1]), dtype=h.dtype, device=h.device)
-                lo = 0
-                for e, cnt in enumerate(host):
-                    if cnt:
-                        torch.mm(y[lo:lo + cnt], self.w_down[e].t(), out=ys[lo:lo + cnt])
-                        lo += cnt
+                for e in range(E):
+                    lo, hi = bounds[e], bounds[e + 1]
+                    if hi > lo:
+                        torch.mm(y[lo:hi], self.w_down[e].t(), out=ys[lo:hi])
         shared = None
         if self.ws_gu is not None:
             shared = F.linear(mixer_ops.clamped_glu(F.linear(h, self.ws_gu), self.shared_limit, GLU_ALPHA), self.ws_down)

@@ -585,10 +585,15 @@ def qknorm_rotary_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_no
 
 @_timed
 def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: torch.Tensor, k_scale: float,
-                   state: torch.Tensor, seqs: torch.Tensor) -> torch.Tensor:
+                   state: torch.Tensor, seqs: torch.Tensor, plan=None) -> torch.Tensor:
     """Fixed-decay linear attention over each sequence's tokens: ``S <- decay[h] S + (k_scale k) v^T``, ``o = S^T q``;
     ``state`` fp32 ``[slots, H, dk, dv]`` is read (unless the sequence is fresh) and written back.  ``q / k [n, H*dk]``
-    and ``v [n, H*dv]`` are column slices of ONE tensor.  Returns fp32 ``[n, H, dv]``."""
+    and ``v [n, H*dv]`` are column slices of ONE tensor.  Returns fp32 ``[n, H, dv]``.
+
+    ``plan`` (``RaggedBatchState.scan_plan()``; None: every sequence runs token by token in one launch) names the long
+    portions of the step as parallel segments: each segment runs as a fresh sequence against a scratch state, one launch
+    chains the segments' end states into the state at every segment's start and the sequence's final state, and one adds
+    what each token missed, ``decay^(t - t0 + 1) P^T q_t``.  Short sequences of the same step run as before."""
     _need_cuda(q, k, v, decay, state, seqs)
     n = q.shape[0]
     _, H, dk, dv = state.shape
@@ -603,10 +608,26 @@ def retention_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, decay: tor
         raise ValueError("decay is contiguous fp32 [H]")
     _check_seqs(seqs)
     o = torch.empty((n, H, dv), dtype=torch.float32, device=q.device)
-    rc = _lib_().b200_retention_scan(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), stride, decay.data_ptr(),
-                                     float(k_scale), state.data_ptr(), seqs.data_ptr(), seqs.shape[0], H, dk, dv,
-                                     DTYPE_ID[q.dtype], _stream())
-    _lib.check_mixers(rc, "b200_retention_scan")
+    lib, dt, st = _lib_(), DTYPE_ID[q.dtype], _stream()
+
+    def scan(into: torch.Tensor, table: torch.Tensor) -> None:
+        rc = lib.b200_retention_scan(o.data_ptr(), q.data_ptr(), k.data_ptr(), v.data_ptr(), stride, decay.data_ptr(),
+                                     float(k_scale), into.data_ptr(), table.data_ptr(), table.shape[0], H, dk, dv, dt, st)
+        _lib.check_mixers(rc, "b200_retention_scan")
+
+    if plan is None:
+        scan(state, seqs)
+        return o
+    if plan.direct is not None:
+        scan(state, plan.direct)
+    seg_state = torch.empty((plan.segs.shape[0], H, dk, dv), dtype=torch.float32, device=q.device)
+    scan(seg_state, plan.segs)
+    rc = lib.b200_retention_carry(state.data_ptr(), seg_state.data_ptr(), plan.parents.data_ptr(), plan.parents.shape[0],
+                                  plan.segs.data_ptr(), decay.data_ptr(), H, dk, dv, st)
+    _lib.check_mixers(rc, "b200_retention_carry")
+    rc = lib.b200_retention_apply_carry(o.data_ptr(), q.data_ptr(), stride, seg_state.data_ptr(), plan.segs.data_ptr(),
+                                        plan.segs.shape[0], decay.data_ptr(), H, dk, dv, dt, st)
+    _lib.check_mixers(rc, "b200_retention_apply_carry")
     return o
 
 

@@ -168,6 +168,15 @@ class PagedLayerKV:
 
 
 @dataclass
+class ScanPlan:
+    """Long portions of a step as parallel segments; see ``RaggedBatchState.scan_plan``."""
+
+    direct: Optional[torch.Tensor]
+    segs: torch.Tensor
+    parents: torch.Tensor
+
+
+@dataclass
 class RaggedBatchState:
     """Device-side description of one PACKED step: row ``n`` of every activation is one token, the tokens of a
     sequence are consecutive and in order, and sequences may bring any number of tokens (a prompt portion, or one
@@ -181,6 +190,7 @@ class RaggedBatchState:
     spans          host list of (first row, token count, block-table row, tokens of the sequence before this step)
     v_first        values the first value-mixing attention layer stored for this step's tokens (set by that layer)
     pending_norm   the next sublayer's normed input when the previous layer already computed it in its epilogue
+    scan_host      the rows of ``scan_seqs`` as a host list (what ``scan_plan`` cuts long portions from)
     """
 
     tok_pos: torch.Tensor
@@ -192,6 +202,7 @@ class RaggedBatchState:
     v_first: Optional[torch.Tensor] = None
     pending_norm: Optional[torch.Tensor] = None
     _tiles: Optional[dict] = None
+    scan_host: Optional[list] = None
 
     def max_context(self) -> int:
         """Tokens of the longest sequence of the step, this step's included."""
@@ -209,6 +220,31 @@ class RaggedBatchState:
     def prompt_tiles(self, at_least: int, cap: int):
         """Tiles of up to ``cap`` tokens over the portions of ``at_least`` tokens or more (tensor-core prompt kernel)."""
         return self._plan(("prompt", cap, at_least), cap, lambda count: count >= at_least)
+
+    def scan_plan(self, segment: int = 256, at_least: int = 512):
+        """For recurrences whose carry can be added afterwards (a fixed decay): the step's portions of ``at_least`` tokens
+        or more cut into segments of ``segment`` tokens, or None when the step has none.  ``.segs`` int32 ``[n, 4]`` are
+        scan rows (first row, count, scratch slot = the segment's index, fresh = 1), ``.parents`` int32 ``[m, 4]`` =
+        (first segment, segments, state slot, fresh), ``.direct`` the scan rows of the step's other sequences (or None).
+        How a portion is cut depends on its own length only."""
+        if self.scan_host is None or not any(count >= at_least for _f, count, _s, _fr in self.scan_host):
+            return None
+        if self._tiles is None:
+            self._tiles = {}
+        key = ("scan", segment, at_least)
+        if key not in self._tiles:
+            direct, segs, parents = [], [], []
+            for first, count, slot, fresh in self.scan_host:
+                if count < at_least:
+                    direct.append((first, count, slot, fresh))
+                    continue
+                parents.append((len(segs), (count + segment - 1) // segment, slot, fresh))
+                for lo in range(0, count, segment):
+                    segs.append((first + lo, min(segment, count - lo), len(segs), 1))
+            table = torch.tensor(direct + segs + parents, dtype=torch.int32).to(self.tok_pos.device, non_blocking=True)
+            a, b = len(direct), len(direct) + len(segs)
+            self._tiles[key] = ScanPlan(table[:a] if a else None, table[a:b], table[b:])
+        return self._tiles[key]
 
     def _plan(self, key, cap: int, keep):
         if self._tiles is None:

@@ -208,6 +208,7 @@ class RaggedStepEngine:
             scan_seqs=up(np.asarray(scans, dtype=np.int32)),
             spans=spans,
             tok_row=up(np.repeat(np.arange(len(spans), dtype=np.int32), [sp[1] for sp in spans])),
+            scan_host=scans,
         )
         h = up(np.asarray(ids, dtype=np.int64))
         for si, shard in enumerate(self.shards):

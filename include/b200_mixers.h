@@ -221,6 +221,19 @@ int b200_retention_scan(float* o_raw, const void* q, const void* k, const void* 
                         float k_scale, float* state, const int32_t* seqs, int n_seqs, int H, int dk, int dv, int dtype,
                         void* stream);
 
+/* Long portions in parallel.  Run b200_retention_scan over SEGMENTS of a portion as if each were a fresh sequence with a
+ * slot of its own in a scratch state tensor seg_state [n_segs, H, dk, dv]; then
+ *   b200_retention_carry        walks every parent's segments (parents int32 [n_parents, 4] = first segment, segments,
+ *                               state slot, fresh): P_0 = the carried state (0 if fresh), P_(j+1) = decay^(n_j) P_j + E_j;
+ *                               seg_state[j] becomes P_j, the parent's slot the final state;
+ *   b200_retention_apply_carry  o_t += decay^(t - t0 + 1) P_j^T q_t for every token of every segment.
+ * seg_spans are the SeqSpan rows the scan ran with. */
+int b200_retention_carry(float* state, float* seg_state, const int32_t* parents, int n_parents, const int32_t* seg_spans,
+                         const float* decay, int H, int dk, int dv, void* stream);
+int b200_retention_apply_carry(float* o_raw, const void* q, int64_t in_stride, const float* seg_state,
+                               const int32_t* seg_spans, int n_segs, const float* decay, int H, int dk, int dv, int dtype,
+                               void* stream);
+
 /* out[n, h*dv + i] = x[n][h][i] * rsqrt(mean_i x^2 + eps) * weight[i] * act(gate[n, h*dv + i]) * out_scale; weight and
  * gate may be NULL; gate_act 0: sigmoid, 1: SiLU.  x fp32 [n, H, dv]; out T with row stride out_stride. */
 int b200_head_norm_act_gate(void* out, int64_t out_stride, const float* x, const void* weight, const void* gate,

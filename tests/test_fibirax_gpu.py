@@ -296,6 +296,45 @@ def test_retention_state_through_portions_and_slots(H, dk, dv):
     close(o[9:].cpu(), R.retention_scan(*args, state=S_ref)[0], 2e-5)
 
 
+@pytest.mark.parametrize("segment,at_least,counts", [(16, 32, (33, 5, 65, 1, 32)), (256, 512, (600, 3, 512)), (64, 64, (200,))])
+def test_retention_long_portions_as_parallel_segments(segment, at_least, counts):
+    from dgi_b200 import mixer_ops as M
+    from dgi_b200.paged_layer import RaggedBatchState
+
+    g = torch.Generator().manual_seed(sum(counts))
+    H, dk, dv = 2, 40, 33
+    decay = [1.0 - 2.0 ** -9, 0.8]
+    n = sum(counts)
+    row = 0.3 * torch.randn(n, 2 * H * dk + H * dv, generator=g)
+    drow = row.to(DEV)
+    dq, dk_, dv_ = drow[:, :H * dk], drow[:, H * dk:2 * H * dk], drow[:, 2 * H * dk:]
+    carried = torch.randn(len(counts), H, dk, dv, generator=g)
+    state = carried.to(DEV).clone()
+    dec = torch.tensor(decay, dtype=torch.float32, device=DEV)
+    spans, at = [], 0
+    for i, c in enumerate(counts):
+        spans.append((at, c, i, i % 2))                        # every second sequence is fresh, the others continue
+        at += c
+    zero = torch.zeros(1, dtype=torch.int32, device=DEV)
+    st = RaggedBatchState(tok_pos=zero, slot_mapping=zero, block_tables=zero, scan_seqs=seqs_of(spans), spans=[], scan_host=spans)
+    plan = st.scan_plan(segment, at_least)
+    assert plan is not None and st.scan_plan(segment, at_least) is plan
+    assert (plan.direct is None) == all(c >= at_least for c in counts)
+    assert plan.parents.shape[0] == sum(c >= at_least for c in counts)
+    assert plan.segs.shape[0] == sum((c + segment - 1) // segment for c in counts if c >= at_least)
+    o = M.retention_scan(dq, dk_, dv_, dec, 0.5, state, st.scan_seqs, plan=plan).cpu()
+    for first, c, slot, fresh in spans:
+        e = row[first:first + c].to(F64)
+        ref, S = R.retention_scan(e[:, :H * dk].view(c, H, dk), e[:, H * dk:2 * H * dk].view(c, H, dk) * 0.5,
+                                  e[:, 2 * H * dk:].view(c, H, dv), decay, state=None if fresh else carried[slot].to(F64))
+        close(o[first:first + c], ref, 3e-5)
+        close(state[slot].cpu(), S, 3e-5)
+    # a step without long portions has no plan
+    st2 = RaggedBatchState(tok_pos=zero, slot_mapping=zero, block_tables=zero, scan_seqs=seqs_of(spans), spans=[],
+                           scan_host=[(0, 5, 0, 1)])
+    assert st2.scan_plan(segment, at_least) is None
+
+
 def test_retention_keeps_one_far_token_among_hundreds():
     from dgi_b200 import mixer_ops as M
 
@@ -482,6 +521,20 @@ def test_portions_of_any_size_down_to_two_tokens(cfg):
             at += c
         engine.finish("a")
         close(torch.cat(got).cpu(), ref[:at], 3e-5)
+
+
+def test_long_prompt_whole_and_in_two_portions():
+    """Portions of 512 tokens and more run their retention as parallel segments; shorter ones token by token."""
+    cfg = CFG_B
+    engine, tensors = build(cfg, max_tokens=1024, max_seqs=2)
+    toks = tokens(640, cfg["vocab"], 16)
+    want = [0, 255, 256, 511, 512, 600, 639]
+    ref = R.forward(cfg, tensors, toks)[want]
+    close(whole(engine, "a", toks, want), ref, 3e-5)
+    got = [engine.step([("b", toks[:100], [0])]), engine.step([("b", toks[100:630], [155, 156, 411, 412, 500]), ("c", toks[:3], [])]),
+           engine.step([("b", toks[630:], [9])])]
+    engine.release()
+    close(torch.cat(got).cpu(), ref, 3e-5)
 
 
 def test_mixed_batches_match_each_request_alone_and_reuse_pages_and_slots():
