@@ -188,7 +188,7 @@ class ParallelMixer(nn.Module):
         # right: retention over the state slots
         o = mixer_ops.retention_scan(proj[:, c[3]:c[3] + Hr * dkr], proj[:, c[4]:c[4] + Hr * dkr],
                                      proj[:, c[5]:c[5] + Hr * dvr], self.decay, dkr ** -0.5, cache.rstate, st.scan_seqs,
-                                     plan=st.scan_plan())
+                                     plan=st.scan_plan(ctas_per_seq=Hr * ((dvr + 31) // 32)))
         mixer_ops.head_norm_act_gate(o, None, proj[:, c[6]:c[6] + Hr * dvr], self.eps, h.dtype, gate_act="silu",
                                      out_scale=self.right_gain, out=buf[:, self.Kl:self.Kl + self.Kr])
         return F.linear(buf, self.w_out)

@@ -221,14 +221,21 @@ class RaggedBatchState:
         """Tiles of up to ``cap`` tokens over the portions of ``at_least`` tokens or more (tensor-core prompt kernel)."""
         return self._plan(("prompt", cap, at_least), cap, lambda count: count >= at_least)
 
-    def scan_plan(self, segment: int = 256, at_least: int = 512):
+    def scan_plan(self, ctas_per_seq: int = 0, segment: int = 0, at_least: int = 512):
         """For recurrences whose carry can be added afterwards (a fixed decay): the step's portions of ``at_least`` tokens
-        or more cut into segments of ``segment`` tokens, or None when the step has none.  ``.segs`` int32 ``[n, 4]`` are
-        scan rows (first row, count, scratch slot = the segment's index, fresh = 1), ``.parents`` int32 ``[m, 4]`` =
-        (first segment, segments, state slot, fresh), ``.direct`` the scan rows of the step's other sequences (or None).
-        How a portion is cut depends on its own length only."""
+        or more cut into segments of ``segment`` tokens, or None when the step has none or when its sequences fill the
+        GPU as they are (``ctas_per_seq``: CTAs the scan launches per sequence; 0 = unknown, always cut).  ``.segs`` int32
+        ``[n, 4]`` are scan rows (first row, count, scratch slot = the segment's index, fresh = 1), ``.parents`` int32
+        ``[m, 4]`` = (first segment, segments, state slot, fresh), ``.direct`` the scan rows of the step's other sequences
+        (or None).  Measured on B200: the segments pay below about one CTA per SM (a lone 2048-token prompt: 3.5 x), and
+        cost time once the token-by-token launch has two CTAs per SM."""
         if self.scan_host is None or not any(count >= at_least for _f, count, _s, _fr in self.scan_host):
             return None
+        ctas = ctas_per_seq * len(self.scan_host)
+        if ctas > 160:
+            return None
+        if segment <= 0:
+            segment = 128 if ctas <= 64 else 256
         if self._tiles is None:
             self._tiles = {}
         key = ("scan", segment, at_least)

@@ -317,8 +317,8 @@ def test_retention_long_portions_as_parallel_segments(segment, at_least, counts)
         at += c
     zero = torch.zeros(1, dtype=torch.int32, device=DEV)
     st = RaggedBatchState(tok_pos=zero, slot_mapping=zero, block_tables=zero, scan_seqs=seqs_of(spans), spans=[], scan_host=spans)
-    plan = st.scan_plan(segment, at_least)
-    assert plan is not None and st.scan_plan(segment, at_least) is plan
+    plan = st.scan_plan(0, segment, at_least)
+    assert plan is not None and st.scan_plan(0, segment, at_least) is plan
     assert (plan.direct is None) == all(c >= at_least for c in counts)
     assert plan.parents.shape[0] == sum(c >= at_least for c in counts)
     assert plan.segs.shape[0] == sum((c + segment - 1) // segment for c in counts if c >= at_least)
@@ -332,7 +332,8 @@ def test_retention_long_portions_as_parallel_segments(segment, at_least, counts)
     # a step without long portions has no plan
     st2 = RaggedBatchState(tok_pos=zero, slot_mapping=zero, block_tables=zero, scan_seqs=seqs_of(spans), spans=[],
                            scan_host=[(0, 5, 0, 1)])
-    assert st2.scan_plan(segment, at_least) is None
+    assert st2.scan_plan(0, segment, at_least) is None
+    assert st.scan_plan(1000, segment, at_least) is None          # sequences that fill the GPU as they are stay whole
 
 
 def test_retention_keeps_one_far_token_among_hundreds():
