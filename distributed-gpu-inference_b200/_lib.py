@@ -179,7 +179,7 @@ MIXER_SIGNATURES = {
                 c_float, c_int, c_int, c_int, c_void_p]),
     "b200_cast_rows": (c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p]),
     "b200_softmax_group_topk": (
-        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_gather_rows": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_void_p]),
     "b200_weighted_expert_combine": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int,
@@ -229,7 +229,7 @@ def check(rc: int, what: str) -> None:
 
 
 def _build_mixers() -> None:
-    """Compile libb200_mixers.so in-tree (one nvcc call, under a minute).  A checkout without built files compiles it
+    """Compile libb200_mixers.so in-tree (its sources in parallel, under a minute).  A checkout without built files compiles it
     at first use; concurrent callers are serialised by a lock file and the library appears atomically."""
     import fcntl
     import subprocess

@@ -444,7 +444,8 @@ __device__ __forceinline__ void warp_argmax(float& best, int& bi) {
 
 __global__ void __launch_bounds__(kRouteWarps * 32)
 softmax_group_topk_kernel(int32_t* __restrict__ ids, float* __restrict__ weights, const float* __restrict__ logits,
-                          const float* __restrict__ correction, int n_tok, int E, int top, int groups, int keep) {
+                          const float* __restrict__ correction, float sum_floor, int n_tok, int E, int top, int groups,
+                          int keep) {
   extern __shared__ float rt_sm[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tok = blockIdx.x * kRouteWarps + warp;
@@ -522,7 +523,7 @@ softmax_group_topk_kernel(int32_t* __restrict__ ids, float* __restrict__ weights
     __syncwarp();
   }
   if (lane == 0) {
-    const float inv = 1.0f / (wsum + 1e-20f);
+    const float inv = 1.0f / (wsum + sum_floor);
     for (int r = 0; r < top; ++r) weights[static_cast<int64_t>(tok) * top + r] *= inv;
   }
 }
@@ -698,8 +699,8 @@ int b200_cast_rows(void* out, const float* x, int64_t n, int dtype, void* stream
   });
 }
 
-int b200_softmax_group_topk(int32_t* ids, float* weights, const float* logits, const float* correction, int n_tok, int E,
-                            int top, int groups, int keep, void* stream) {
+int b200_softmax_group_topk(int32_t* ids, float* weights, const float* logits, const float* correction, float sum_floor,
+                            int n_tok, int E, int top, int groups, int keep, void* stream) {
   if (n_tok < 0 || E <= 0 || top <= 0 || top > E || groups < 1 || keep < 1 || keep > groups || E % groups)
     return fail(B200_EINVAL, "b200_softmax_group_topk: bad sizes");
   if (groups > 1 && keep < groups && static_cast<int64_t>(keep) * (E / groups) < top)
@@ -711,7 +712,7 @@ int b200_softmax_group_topk(int32_t* ids, float* weights, const float* logits, c
   auto kern = softmax_group_topk_kernel;
   if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
   kern<<<(n_tok + kRouteWarps - 1) / kRouteWarps, kRouteWarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(
-      ids, weights, logits, correction, n_tok, E, top, groups, keep);
+      ids, weights, logits, correction, sum_floor, n_tok, E, top, groups, keep);
   return check_launch("b200_softmax_group_topk");
 }
 

@@ -47,7 +47,7 @@ from .sanesun_layer import PlainRMSNorm, ScaledFloatEmbedding, _pad8
 from .worker.distributed.model_shard import ModelShard
 
 GLU_ALPHA = 1.702          # the experts' gate is g * sigmoid(1.702 g); fixed by the design
-WEIGHT_SUM_FLOOR = 1e-20   # added to the sum of the chosen scores (inside the routing kernel)
+WEIGHT_SUM_FLOOR = 1e-20   # added to the sum of the chosen scores before the weights are divided by it
 
 
 class FibiraxConfig:
@@ -237,7 +237,8 @@ class GroupedSoftmaxMoE(nn.Module):
     def forward(self, h: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         """``h``: the sublayer's input in the experts' dtype, ``x``: the same rows in fp32 (the residual)."""
         n, top, E = h.shape[0], self.top, self.E
-        ids, w = mixer_ops.softmax_group_topk(F.linear(x, self.w_router), self.correction, top, self.groups, self.keep)
+        ids, w = mixer_ops.softmax_group_topk(F.linear(x, self.w_router), self.correction, top, self.groups, self.keep,
+                                              sum_floor=WEIGHT_SUM_FLOOR)
         # rows in expert order; where each expert's rows start comes from the sorted ids themselves (a search, not a
         # count: no value ever travels to the host)
         sorted_ids, order = torch.sort(ids.reshape(-1).to(torch.int64), stable=True)

@@ -695,10 +695,10 @@ def cast_rows(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
 
 @_timed
 def softmax_group_topk(logits: torch.Tensor, correction: Optional[torch.Tensor], top: int, groups: int = 1,
-                       keep: int = 1):
+                       keep: int = 1, sum_floor: float = 0.0):
     """fp32 ``[n, E]`` router logits -> ``(ids int32 [n, top], weights fp32 [n, top])``: softmax scores, the choice by
-    score + ``correction`` inside the ``keep`` best of ``groups`` expert groups, weights = chosen scores over their
-    sum."""
+    score + ``correction`` inside the ``keep`` best of ``groups`` expert groups, weights = chosen scores over (their
+    sum + ``sum_floor``)."""
     _need_cuda(logits)
     if logits.dtype != torch.float32 or not logits.is_contiguous() or logits.dim() != 2:
         raise ValueError("router logits are contiguous fp32 [n, E]")
@@ -708,8 +708,8 @@ def softmax_group_topk(logits: torch.Tensor, correction: Optional[torch.Tensor],
         raise ValueError("correction is contiguous fp32 [E]")
     ids = torch.empty((n, top), dtype=torch.int32, device=logits.device)
     w = torch.empty((n, top), dtype=torch.float32, device=logits.device)
-    rc = _lib_().b200_softmax_group_topk(ids.data_ptr(), w.data_ptr(), logits.data_ptr(), _ptr(correction), n, E, int(top),
-                                         int(groups), int(keep), _stream())
+    rc = _lib_().b200_softmax_group_topk(ids.data_ptr(), w.data_ptr(), logits.data_ptr(), _ptr(correction),
+                                         float(sum_floor), n, E, int(top), int(groups), int(keep), _stream())
     _lib.check_mixers(rc, "b200_softmax_group_topk")
     return ids, w
 

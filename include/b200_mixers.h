@@ -251,9 +251,9 @@ int b200_cast_rows(void* out, const float* x, int64_t n, int dtype, void* stream
 
 /* Routing with softmax scores s over E router outputs: choice scores c = s + correction (NULL: c = s); the experts form
  * `groups` equal groups of neighbours, only the `keep` groups with the largest best c can be chosen; the `top` largest c
- * among them are chosen (ties: lowest index); weights = their s over the sum of their s (+ 1e-20). */
-int b200_softmax_group_topk(int32_t* ids, float* weights, const float* logits, const float* correction, int n_tok, int E,
-                            int top, int groups, int keep, void* stream);
+ * among them are chosen (ties: lowest index); weights = their s over (the sum of their s + sum_floor). */
+int b200_softmax_group_topk(int32_t* ids, float* weights, const float* logits, const float* correction, float sum_floor,
+                            int n_tok, int E, int top, int groups, int keep, void* stream);
 
 /* xs[r] = h[src[r] / top]: the expert-sorted rows, unscaled. */
 int b200_gather_rows(void* xs, const void* h, const int64_t* src, int64_t n_rows, int top, int width, int dtype,
