@@ -184,6 +184,34 @@ MIXER_SIGNATURES = {
     "b200_weighted_expert_combine": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_int, c_int,
                 c_void_p]),
+    # chunked masks, values inside wider rows, several score maps per value head (csrc/b200_hybrid_ops.cu)
+    "b200_mixed_paged_attn_ext": (
+        c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int, c_int, c_int,
+                c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_mixed_prompt_attn_ext": (
+        c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
+                c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int,
+                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
+    "b200_qknorm_rotary_append_ext": (
+        c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
+                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int,
+                c_void_p]),
+    # token shift, gated post-norm sublayers, a decoupled rotated key part (csrc/b200_gated_ops.cu)
+    "b200_token_shift": (
+        c_int, [c_void_p, c_int64, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_latent_rotary_append": (
+        c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_float, c_void_p,
+                c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "b200_head_diff_norm": (
+        c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_float, c_float, c_float, c_int64, c_int, c_int, c_int,
+                c_int, c_void_p]),
+    "b200_gated_postnorm_residual": (
+        c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_float, c_int, c_int,
+                c_int, c_void_p]),
+    "b200_relu_squared": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "b200_gated_table_rows": (
+        c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),
 }
 
 _lock = threading.Lock()
@@ -239,7 +267,7 @@ def _build_mixers() -> None:
         fcntl.flock(lock, fcntl.LOCK_EX)
         if os.path.exists(MIXER_LIB_PATH):
             return
-        proc = subprocess.run(["make", "-j3", "-C", csrc, "mixers"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
+        proc = subprocess.run(["make", "-j4", "-C", csrc, "mixers"], stdout=subprocess.PIPE, stderr=subprocess.STDOUT)
         if proc.returncode != 0 or not os.path.exists(MIXER_LIB_PATH):
             raise B200LibraryError("building libb200_mixers.so failed:\n" + proc.stdout.decode(errors="replace")[-4000:])
 

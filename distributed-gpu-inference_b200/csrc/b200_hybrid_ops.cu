@@ -259,7 +259,17 @@ struct AttnArgs {
   float scale; int window, keep_first, unrotate, interleaved; double rot_base;
   int H, G, dk, dv, block_size;
   float softcap;   // > 0: score <- softcap * tanh(score / softcap), after the head mixing and before the mask
+  int chunk = 0;   // > 0: a position sees only the keys of its own block of `chunk` positions (counted from 0)
+  int v_row = 0;   // elements between value rows in v_pool (the value size unless the values are the first columns of wider rows)
+  int v_div = 1;   // value head = key head / v_div (several key heads read one value head)
 };
+
+// first key a position sees (the kept first tokens of a window aside)
+__device__ __forceinline__ int first_visible(const AttnArgs& A, int p) {
+  int lo = A.window > 0 ? max(0, p - A.window + 1) : 0;
+  if (A.chunk > 0) lo = max(lo, (p / A.chunk) * A.chunk);
+  return lo;
+}
 
 constexpr int kAttnWarpsRow = 4;
 
@@ -307,8 +317,9 @@ mixed_paged_attn_kernel(const AttnArgs A) {
   __syncthreads();
   const int p = A.tok_pos[n];
   const int32_t* table = A.block_tables + static_cast<int64_t>(A.tok_row[n]) * A.table_stride;
-  const int lo = A.window > 0 ? max(0, p - A.window + 1) : 0;
+  const int lo = first_visible(A, p);
   const int kf = A.window > 0 ? min(A.keep_first, lo) : 0;   // kept first tokens that the window no longer covers
+  const int Gv = G / A.v_div;
   const int nA = (kf + 31) >> 5;
   const int cB0 = max(nA, lo >> 5), cB1 = p >> 5;
   const int n_chunks = nA + (cB1 - cB0 + 1);
@@ -327,9 +338,13 @@ mixed_paged_attn_kernel(const AttnArgs A) {
   for (int idx = warp; idx < n_chunks; idx += kAttnWarpsRow) {
     const int c = idx < nA ? idx : cB0 + idx - nA;
     const int j = c * 32 + lane;
-    const bool valid = j <= p && (A.window <= 0 || p - j < A.window || j < A.keep_first);
-    int base = 0;                                            // row of the key in head 0 of its block
-    if (valid) base = (table[j / bs] * G) * bs + j % bs;
+    const bool valid = j <= p && (j >= lo || (A.window > 0 && j < A.keep_first));
+    int base = 0, vrow0 = 0;                                 // row of the key / the value in head 0 of its block
+    if (valid) {
+      const int blk = table[j / bs];
+      base = (blk * G) * bs + j % bs;
+      vrow0 = (blk * Gv) * bs + j % bs;
+    }
     __syncwarp();
     if (valid) {
       for (int hh = 0; hh < nhs; ++hh) {
@@ -366,16 +381,16 @@ mixed_paged_attn_kernel(const AttnArgs A) {
       }
     }
     for (int jj = 0; jj < 32; ++jj) {
-      const int vbase = __shfl_sync(0xffffffffu, base, jj);
+      const int vbase = __shfl_sync(0xffffffffu, vrow0, jj);
       float vv[DVC];
       int g_have = -1;
 #pragma unroll
       for (int hl = 0; hl < HP; ++hl) {
         const float pj = __shfl_sync(0xffffffffu, pr[hl], jj);
         if (pj != 0.f) {         // uniform over the warp; also skips heads past H and keys that are masked
-          const int g = (h0 + hl) / rep;
+          const int g = (h0 + hl) / rep / A.v_div;
           if (g != g_have) {
-            const T* vr = vp + static_cast<int64_t>(vbase + g * bs) * dv;
+            const T* vr = vp + static_cast<int64_t>(vbase + g * bs) * A.v_row;
 #pragma unroll
             for (int cc = 0; cc < DVC; ++cc) vv[cc] = (lane + 32 * cc < dv) ? Cvt<T>::to_f32(vr[lane + 32 * cc]) : 0.f;
             g_have = g;
@@ -518,10 +533,11 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
   const bool mixed = A.talk != nullptr;
   const int g_lo = mixed ? 0 : h0 / rep;
   const int Gs = (mixed ? G - 1 : min(H - 1, h0 + HC - 1) / rep) - g_lo + 1;   // kv heads staged per tile
-  const int ks = dk + 8, vs = DVP + 8;                                          // row strides in elements
   const T* kp = static_cast<const T*>(A.k_pool);
   const T* vp = static_cast<const T*>(A.v_pool);
-  const bool alias = (A.v_pool == A.k_pool) && dk == DVP;
+  const bool alias = (A.v_pool == A.k_pool) && A.v_div == 1 && DVP <= dk;   // the values are the first columns of the staged key rows
+  const int ks = dk + 8, vs = alias ? ks : DVP + 8;                             // row strides in elements
+  const int Gv = G / A.v_div;
   const int stage_elems = Gs * kTcKeys * (ks + (alias ? 0 : vs));                 // one stage: K rows, then V rows
   T* stage0 = reinterpret_cast<T*>(tc_smem);
   const T* Ks = stage0;                                                         // the stage being computed on
@@ -530,7 +546,7 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
   float* talk_s = raw + (mixed ? H * kTcRows * kTcRawStride : 0);                               // [HC][H]
   const int p0 = A.tok_pos[row0], p_last = p0 + cnt - 1;
   const int32_t* table = A.block_tables + static_cast<int64_t>(trow) * A.table_stride;
-  const int lo0 = A.window > 0 ? max(0, p0 - A.window + 1) : 0;
+  const int lo0 = first_visible(A, p0);
   const int kf = A.window > 0 ? min(A.keep_first, lo0) : 0;
   const int nA = (kf + kTcKeys - 1) / kTcKeys;
   const int cB0 = max(nA, lo0 / kTcKeys), cB1 = p_last / kTcKeys;
@@ -599,7 +615,7 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
       for (int e = threadIdx.x; e < Gs * kTcKeys * vch; e += blockDim.x) {
         const int ch = e % vch, r = e / vch, key = r % kTcKeys, gi = r / kTcKeys, j = j0 + key;
         const bool ok = j <= p_last;
-        const T* src = ok ? vp + (static_cast<int64_t>(table[j / bs] * G + g_lo + gi) * bs + j % bs) * dv + ch * 8 : vp;
+        const T* src = ok ? vp + (static_cast<int64_t>(table[j / bs] * Gv + (g_lo + gi) / A.v_div) * bs + j % bs) * A.v_row + ch * 8 : vp;
         stage16(Vd + r * vs + ch * 8, src, ok);
       }
     }
@@ -663,13 +679,14 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
       for (int half = 0; half < 2; ++half) {
         const int row = qr + 8 * half, p = p0 + row;
         const bool row_ok = row < cnt;
+        const int lo_p = first_visible(A, p);
         float mx = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
 #pragma unroll
           for (int e = 0; e < 2; ++e) {
             const int j = j0 + nt * 8 + qc + e;
-            const bool ok = row_ok && j <= p && (A.window <= 0 || p - j < A.window || j < A.keep_first);
+            const bool ok = row_ok && j <= p && (j >= lo_p || (A.window > 0 && j < A.keep_first));
             if (A.softcap > 0.f) s[nt][2 * half + e] = soft_cap(s[nt][2 * half + e], A.softcap, cap2);
             if (!ok) s[nt][2 * half + e] = -INFINITY;
             mx = fmaxf(mx, s[nt][2 * half + e]);
@@ -886,7 +903,7 @@ inline bool tc_plan(int H, int G, int dk, int dv, bool has_talk, bool same_pool,
   // head per warp, which halves the staged kv heads per CTA and lets two CTAs share an SM
   const int hw = (dv8 <= 16 && H > kTcWarps && (has_talk || H / G > kTcWarps)) ? 2 : 1;
   const int gs = has_talk ? G : std::min(G, (kTcWarps * hw + H / G - 1) / (H / G) + 1);
-  const bool alias = same_pool && dk == dvp;
+  const bool alias = same_pool && dvp <= dk;
   size_t stage = static_cast<size_t>(gs) * kTcKeys * (dk + 8) * 2;
   if (!alias) stage += static_cast<size_t>(gs) * kTcKeys * (dvp + 8) * 2;
   size_t rest = 0;
@@ -1266,7 +1283,21 @@ int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_st
                           const int32_t* tok_pos, int n_tok, const float* talk, const float* sink, float scale,
                           float softcap, int window, int keep_first, int unrotate, int interleaved, float rot_base, int H,
                           int G, int dk, int dv, int block_size, int dtype, void* stream) {
-  if (n_tok < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || block_size <= 0)
+  return b200_mixed_paged_attn_ext(out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride,
+                                   k_pool, v_pool, block_tables, table_stride, tok_row, tok_pos, n_tok, talk, sink, scale,
+                                   softcap, window, keep_first, 0, unrotate, interleaved, rot_base, H, G, dk, dv, dv, 1,
+                                   block_size, dtype, stream);
+}
+
+int b200_mixed_paged_attn_ext(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q,
+                              int64_t q_tok_stride, int64_t q_head_stride, const void* gate, int64_t gate_stride,
+                              const void* k_pool, const void* v_pool, const int32_t* block_tables, int table_stride,
+                              const int32_t* tok_row, const int32_t* tok_pos, int n_tok, const float* talk,
+                              const float* sink, float scale, float softcap, int window, int keep_first, int chunk,
+                              int unrotate, int interleaved, float rot_base, int H, int G, int dk, int dv, int v_row,
+                              int v_div, int block_size, int dtype, void* stream) {
+  if (n_tok < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || block_size <= 0 || chunk < 0 || v_row < dv ||
+      v_div < 1 || G % v_div)
     return fail(B200_EINVAL, "b200_mixed_paged_attn: bad sizes");
   if (dv > 512) return fail(B200_ESHAPE, "b200_mixed_paged_attn: value size %d beyond 512", dv);
   if (n_tok == 0) return 0;
@@ -1274,7 +1305,7 @@ int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_st
     return fail(B200_EINVAL, "b200_mixed_paged_attn: null pointer");
   AttnArgs A{out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride, k_pool, v_pool,
              block_tables, table_stride, tok_row, tok_pos, talk, sink, scale, window, keep_first, unrotate, interleaved,
-             static_cast<double>(rot_base), H, G, dk, dv, block_size, softcap};
+             static_cast<double>(rot_base), H, G, dk, dv, block_size, softcap, chunk, v_row, v_div};
   const int dvc = dv <= 64 ? 2 : (dv <= 128 ? 4 : (dv <= 256 ? 8 : 16));
   const int hp = dvc <= 4 ? 8 : (dvc == 8 ? 4 : 2);
   const int nhs = talk ? H : std::min(hp, H);
@@ -1326,6 +1357,21 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
                            float scale, float softcap, int window, int keep_first, const float* value_rot, int interleaved,
                            int H, int G, int dk, int dv, int block_size, int n_splits, float* workspace, int dtype,
                            void* stream) {
+  return b200_mixed_prompt_attn_ext(out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride,
+                                    k_pool, v_pool, block_tables, table_stride, tiles, n_tiles, tok_pos, n_tok, talk, sink,
+                                    scale, softcap, window, keep_first, 0, value_rot, interleaved, H, G, dk, dv, dv, 1,
+                                    block_size, n_splits, workspace, dtype, stream);
+}
+
+int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q,
+                               int64_t q_tok_stride, int64_t q_head_stride, const void* gate, int64_t gate_stride,
+                               const void* k_pool, const void* v_pool, const int32_t* block_tables, int table_stride,
+                               const int32_t* tiles, int n_tiles, const int32_t* tok_pos, int n_tok, const float* talk,
+                               const float* sink, float scale, float softcap, int window, int keep_first, int chunk,
+                               const float* value_rot, int interleaved, int H, int G, int dk, int dv, int v_row, int v_div,
+                               int block_size, int n_splits, float* workspace, int dtype, void* stream) {
+  if (chunk < 0 || v_row < dv || v_row % 8 || v_div < 1 || G % v_div)
+    return fail(B200_EINVAL, "b200_mixed_prompt_attn: bad mask or value layout");
   if (n_tiles < 0 || n_tok < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || block_size <= 0 || n_splits < 1 ||
       n_splits > 64)
     return fail(B200_EINVAL, "b200_mixed_prompt_attn: bad sizes");
@@ -1339,7 +1385,7 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
     return fail(B200_ESHAPE, "b200_mixed_prompt_attn: sizes off the tensor-core grid (dk %d, dv %d)", dk, dv);
   AttnArgs A{out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride, k_pool, v_pool,
              block_tables, table_stride, nullptr, tok_pos, talk, sink, scale, window, keep_first, value_rot != nullptr,
-             interleaved, 0.0, H, G, dk, dv, block_size, softcap};
+             interleaved, 0.0, H, G, dk, dv, block_size, softcap, chunk, v_row, v_div};
   const dim3 grid(n_tiles, (H + kTcWarps * plan.hw - 1) / (kTcWarps * plan.hw), n_splits);
   return hybrid_by_dtype(dtype, "b200_mixed_prompt_attn", [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;

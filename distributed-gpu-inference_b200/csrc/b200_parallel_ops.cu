@@ -62,7 +62,7 @@ qknorm_rotary_append_kernel(T* __restrict__ q, int64_t q_stride, const T* __rest
                             const T* __restrict__ v, int64_t v_stride, const T* __restrict__ qw, const T* __restrict__ kw,
                             float eps, const double* __restrict__ freqs, int rot_dims, int interleaved,
                             T* __restrict__ k_pool, T* __restrict__ v_pool, const int64_t* __restrict__ slot_mapping,
-                            const int32_t* __restrict__ tok_pos, int H, int G, int dk, int dv, int block_size) {
+                            const int32_t* __restrict__ tok_pos, int H, int G, int Gv, int dk, int dv, int block_size) {
   extern __shared__ float qk_sm[];     // cos[rh] sin[rh] slab[warps][dk]
   const int n = blockIdx.x, rh = rot_dims / 2;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -109,9 +109,9 @@ qknorm_rotary_append_kernel(T* __restrict__ q, int64_t q_stride, const T* __rest
   }
   if (slot < 0) return;
   const T* vr = v + static_cast<int64_t>(n) * v_stride;
-  for (int e = threadIdx.x; e < G * dv; e += blockDim.x) {
+  for (int e = threadIdx.x; e < Gv * dv; e += blockDim.x) {
     const int g = e / dv, i = e - g * dv;
-    v_pool[((blk * G + g) * block_size + off) * dv + i] = vr[e];
+    v_pool[((blk * Gv + g) * block_size + off) * dv + i] = vr[e];
   }
 }
 
@@ -568,6 +568,17 @@ int b200_qknorm_rotary_append(void* q, int64_t q_stride, const void* k, int64_t 
                               int interleaved, void* k_pool, void* v_pool, const int64_t* slot_mapping,
                               const int32_t* tok_pos, int n_tok, int H, int G, int dk, int dv, int block_size,
                               int64_t max_blocks, int dtype, void* stream) {
+  return b200_qknorm_rotary_append_ext(q, q_stride, k, k_stride, v, v_stride, q_norm, k_norm, eps, freqs, rot_dims,
+                                       interleaved, k_pool, v_pool, slot_mapping, tok_pos, n_tok, H, G, G, dk, dv, block_size,
+                                       max_blocks, dtype, stream);
+}
+
+int b200_qknorm_rotary_append_ext(void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                                  int64_t v_stride, const void* q_norm, const void* k_norm, float eps, const double* freqs,
+                                  int rot_dims, int interleaved, void* k_pool, void* v_pool, const int64_t* slot_mapping,
+                                  const int32_t* tok_pos, int n_tok, int H, int G, int Gv, int dk, int dv, int block_size,
+                                  int64_t max_blocks, int dtype, void* stream) {
+  if (Gv <= 0) return fail(B200_EINVAL, "b200_qknorm_rotary_append: bad sizes");
   if (n_tok < 0 || H <= 0 || G <= 0 || dk <= 0 || dv <= 0 || block_size <= 0 || max_blocks <= 0)
     return fail(B200_EINVAL, "b200_qknorm_rotary_append: bad sizes");
   if (rot_dims < 0 || rot_dims > dk || (rot_dims & 1)) return fail(B200_ESHAPE, "b200_qknorm_rotary_append: rot_dims %d", rot_dims);
@@ -583,7 +594,7 @@ int b200_qknorm_rotary_append(void* q, int64_t q_stride, const void* k, int64_t 
     kern<<<n_tok, kQkWarps * 32, smem, static_cast<cudaStream_t>(stream)>>>(
         static_cast<T*>(q), q_stride, static_cast<const T*>(k), k_stride, static_cast<const T*>(v), v_stride,
         static_cast<const T*>(q_norm), static_cast<const T*>(k_norm), eps, freqs, rot_dims, interleaved,
-        static_cast<T*>(k_pool), static_cast<T*>(v_pool), slot_mapping, tok_pos, H, G, dk, dv, block_size);
+        static_cast<T*>(k_pool), static_cast<T*>(v_pool), slot_mapping, tok_pos, H, G, Gv, dk, dv, block_size);
     return check_launch("b200_qknorm_rotary_append");
   });
 }

@@ -234,11 +234,21 @@ class GroupedSoftmaxMoE(nn.Module):
             self._ar = torch.arange(max(n, 4096), device=device)
         return self._ar[:n]
 
+    def _route(self, x: torch.Tensor):
+        """``(expert ids int32 [n, top], weights fp32 [n, top])`` from the fp32 residual rows."""
+        return mixer_ops.softmax_group_topk(F.linear(x, self.w_router), self.correction, self.top, self.groups, self.keep,
+                                            sum_floor=WEIGHT_SUM_FLOOR)
+
+    def _activate(self, z: torch.Tensor) -> torch.Tensor:
+        """What stands between an expert's two matrices; subclasses with other experts override this and ``_route``."""
+        if z.shape[0] == 0:
+            return z[:, :z.shape[1] // 2]
+        return mixer_ops.clamped_glu(z, self.limit, GLU_ALPHA)
+
     def forward(self, h: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
         """``h``: the sublayer's input in the experts' dtype, ``x``: the same rows in fp32 (the residual)."""
         n, top, E = h.shape[0], self.top, self.E
-        ids, w = mixer_ops.softmax_group_topk(F.linear(x, self.w_router), self.correction, top, self.groups, self.keep,
-                                              sum_floor=WEIGHT_SUM_FLOOR)
+        ids, w = self._route(x)
         # rows in expert order; where each expert's rows start comes from the sorted ids themselves (a search, not a
         # count: no value ever travels to the host)
         sorted_ids, order = torch.sort(ids.reshape(-1).to(torch.int64), stable=True)
@@ -249,12 +259,12 @@ class GroupedSoftmaxMoE(nn.Module):
             offsets = torch.searchsorted(sorted_ids, self._arange(E + 1, h.device)).to(torch.int32)
             xs = mixer_ops.gather_rows(h, order, top)      # identity rows ride at the end and are never multiplied
             if self.grouped and n * top <= self.GROUPED_MAX_ROWS:
-                y = mixer_ops.clamped_glu(mixer_ops.grouped_linear(xs, self.w_gu, offsets), self.limit, GLU_ALPHA)
+                y = self._activate(mixer_ops.grouped_linear(xs, self.w_gu, offsets))
                 ys = mixer_ops.grouped_linear(y, self.w_down, offsets)
             elif self.grouped and hasattr(torch, "_grouped_mm"):
                 # long prompt steps: the vendor's grouped GEMM, which also reads the offsets on the device
                 ends = offsets[1:]
-                y = mixer_ops.clamped_glu(torch._grouped_mm(xs, self.w_gu.transpose(1, 2), offs=ends), self.limit, GLU_ALPHA)
+                y = self._activate(torch._grouped_mm(xs, self.w_gu.transpose(1, 2), offs=ends))
                 ys = torch._grouped_mm(y, self.w_down.transpose(1, 2), offs=ends)
             else:
                 # fp32, or sizes off the 16-byte grid: one vendor GEMM per expert; the counts come to the host once
@@ -265,7 +275,7 @@ class GroupedSoftmaxMoE(nn.Module):
                     if hi > lo:
                         torch.mm(xs[lo:hi], self.w_gu[e].t(), out=gu[lo:hi])
                 routed = bounds[E]
-                y = mixer_ops.clamped_glu(gu[:routed], self.limit, GLU_ALPHA) if routed else gu[:0, :gu.shape[1] // 2]
+                y = self._activate(gu[:routed])
                 ys = torch.empty((n * top, h.shape[1]), dtype=h.dtype, device=h.device)
                 for e in range(E):
                     lo, hi = bounds[e], bounds[e + 1]

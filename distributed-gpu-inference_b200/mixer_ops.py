@@ -387,21 +387,38 @@ def norm_append(x: torch.Tensor, weight: torch.Tensor, eps: float, pool: torch.T
     _lib.check_mixers(rc, "b200_norm_append")
 
 
+def _value_layout(k_pool: torch.Tensor, v_pool: torch.Tensor, value_width: Optional[int], value_div: int):
+    """``(value size, elements between value rows)`` of an attention call, after checking the pools against each other."""
+    if v_pool.dim() != 4 or v_pool.shape[0] != k_pool.shape[0] or v_pool.shape[2] != k_pool.shape[2]:
+        raise ValueError("the pools must agree on blocks and block size")
+    if value_div < 1 or v_pool.shape[1] * value_div != k_pool.shape[1]:
+        raise ValueError("v_pool holds one head per `value_div` key heads")
+    v_row = v_pool.shape[3]
+    dv = v_row if value_width is None else int(value_width)
+    if dv < 1 or dv > v_row:
+        raise ValueError("value_width exceeds the rows of v_pool")
+    return dv, v_row
+
+
 @_timed
 def mixed_paged_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor,
                           block_tables: torch.Tensor, tok_row: torch.Tensor, tok_pos: torch.Tensor, scale: float,
                           talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, window: int = 0,
                           keep_first: int = 0, unrotate_base: Optional[float] = None, interleaved: bool = False,
-                          gate: Optional[torch.Tensor] = None, softcap: float = 0.0) -> None:
+                          gate: Optional[torch.Tensor] = None, softcap: float = 0.0, chunk: int = 0,
+                          value_width: Optional[int] = None, value_div: int = 1) -> None:
     """Softmax attention of packed query rows over the paged cache.  ``q`` and ``out`` are 3-D ``[n, H, dk | dv]``
     VIEWS with a contiguous last dimension (any token / head strides); ``talk`` fp32 ``[H, H]`` mixes the heads'
     scores before the softmax, ``sink`` fp32 ``[H]`` adds exp(sink) to the denominator, ``window`` > 0 limits a
     position to its last ``window`` tokens plus the sequence's first ``keep_first``, ``unrotate_base`` turns the
     output back by the position over the value width, ``gate`` ``[n, H]`` is a sigmoid gate per head, ``softcap`` > 0
-    bounds the scores by ``softcap * tanh(score / softcap)`` before the mask."""
+    bounds the scores by ``softcap * tanh(score / softcap)`` before the mask, ``chunk`` > 0 lets a position see only
+    the keys of its own block of ``chunk`` positions, ``value_width`` says that the values are the first that many
+    columns of the (wider) rows of ``v_pool``, ``value_div`` that ``v_pool`` holds one value head per that many key
+    heads (several score maps over the same values)."""
     _need_cuda(out, q, k_pool, v_pool, block_tables, tok_row, tok_pos)
     nb, G, bs, dk = k_pool.shape
-    dv = v_pool.shape[3]
+    dv, v_row = _value_layout(k_pool, v_pool, value_width, value_div)
     n, H = q.shape[0], q.shape[1]
     if q.dim() != 3 or q.shape[2] != dk or tuple(out.shape) != (n, H, dv) or q.stride(2) != 1 or out.stride(2) != 1:
         raise ValueError("q must be [n, H, dk] and out [n, H, dv] with contiguous last dimensions")
@@ -415,12 +432,14 @@ def mixed_paged_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tens
             raise ValueError("talk is contiguous fp32 [H, H], sink fp32 [H]")
     if gate is not None and (tuple(gate.shape) != (n, H) or gate.dtype != q.dtype):
         raise ValueError("gate must be [n, H] in the activations' dtype")
-    rc = _lib_().b200_mixed_paged_attn(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0), q.stride(1),
-                                       _ptr(gate), _rows2(gate) if gate is not None else 0, k_pool.data_ptr(),
-                                       v_pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), tok_row.data_ptr(),
-                                       tok_pos.data_ptr(), n, _ptr(talk), _ptr(sink), float(scale), float(softcap),
-                                       int(window), int(keep_first), int(unrotate_base is not None), int(interleaved),
-                                       float(unrotate_base or 0.0), H, G, dk, dv, bs, DTYPE_ID[q.dtype], _stream())
+    rc = _lib_().b200_mixed_paged_attn_ext(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0),
+                                           q.stride(1), _ptr(gate), _rows2(gate) if gate is not None else 0,
+                                           k_pool.data_ptr(), v_pool.data_ptr(), block_tables.data_ptr(),
+                                           block_tables.stride(0), tok_row.data_ptr(), tok_pos.data_ptr(), n, _ptr(talk),
+                                           _ptr(sink), float(scale), float(softcap), int(window), int(keep_first),
+                                           int(chunk), int(unrotate_base is not None), int(interleaved),
+                                           float(unrotate_base or 0.0), H, G, dk, dv, v_row, int(value_div), bs,
+                                           DTYPE_ID[q.dtype], _stream())
     _lib.check_mixers(rc, "b200_mixed_paged_attn")
 
 
@@ -438,15 +457,17 @@ def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Ten
                            block_tables: torch.Tensor, tiles: torch.Tensor, tok_pos: torch.Tensor, scale: float,
                            talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, window: int = 0,
                            keep_first: int = 0, value_rot: Optional[torch.Tensor] = None, interleaved: bool = False,
-                           gate: Optional[torch.Tensor] = None, max_context: int = 0, softcap: float = 0.0) -> None:
+                           gate: Optional[torch.Tensor] = None, max_context: int = 0, softcap: float = 0.0,
+                           chunk: int = 0, value_width: Optional[int] = None, value_div: int = 1) -> None:
     """``mixed_paged_attention`` on the tensor cores for prompt portions and decoded tokens alike (16-bit dtypes, see
     ``mixed_prompt_attention_supported``).  ``tiles`` int32 ``[n_tiles, 3]``: up to ``PROMPT_TILE_TOKENS`` consecutive
     tokens of one sequence each, together covering every row of ``q``; ``value_rot``: the table ``rotary_kv_append``
     returned for this step's tokens; ``max_context``: the longest context of the step (a hint: steps of few tokens over
-    long contexts divide the keys over several CTAs and merge)."""
+    long contexts divide the keys over several CTAs and merge); ``chunk``, ``value_width`` and ``value_div`` as in
+    ``mixed_paged_attention``."""
     _need_cuda(out, q, k_pool, v_pool, block_tables, tiles, tok_pos)
     nb, G, bs, dk = k_pool.shape
-    dv = v_pool.shape[3]
+    dv, v_row = _value_layout(k_pool, v_pool, value_width, value_div)
     n, H = q.shape[0], q.shape[1]
     if q.dim() != 3 or q.shape[2] != dk or tuple(out.shape) != (n, H, dv) or q.stride(2) != 1 or out.stride(2) != 1:
         raise ValueError("q must be [n, H, dk] and out [n, H, dv] with contiguous last dimensions")
@@ -464,19 +485,21 @@ def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Ten
         raise ValueError("gate must be [n, H] in the activations' dtype")
     lib = _lib_()
     seen = min(max_context, window + keep_first + PROMPT_TILE_TOKENS) if window > 0 else max_context
+    if chunk > 0:
+        seen = min(seen, chunk + PROMPT_TILE_TOKENS)
     splits = lib.b200_mixed_prompt_attn_splits(tiles.shape[0], (seen + 31) // 32, H, G, dk, dv, int(talk is not None),
                                                int(k_pool.data_ptr() == v_pool.data_ptr()), int(value_rot is not None),
                                                DTYPE_ID[q.dtype]) if max_context > 0 else 1
     ws = None
     if splits > 1:
         ws = torch.empty(lib.b200_mixed_prompt_attn_workspace(splits, n, H, dv) // 4, dtype=torch.float32, device=q.device)
-    rc = lib.b200_mixed_prompt_attn(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0), q.stride(1),
-                                    _ptr(gate), _rows2(gate) if gate is not None else 0, k_pool.data_ptr(),
-                                    v_pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0), tiles.data_ptr(),
-                                    tiles.shape[0], tok_pos.data_ptr(), n, _ptr(talk), _ptr(sink), float(scale),
-                                    float(softcap), int(window), int(keep_first), _ptr(value_rot), int(interleaved), H, G,
-                                    dk, dv, bs, int(splits),
-                                    _ptr(ws), DTYPE_ID[q.dtype], _stream())
+    rc = lib.b200_mixed_prompt_attn_ext(out.data_ptr(), out.stride(0), out.stride(1), q.data_ptr(), q.stride(0),
+                                        q.stride(1), _ptr(gate), _rows2(gate) if gate is not None else 0, k_pool.data_ptr(),
+                                        v_pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
+                                        tiles.data_ptr(), tiles.shape[0], tok_pos.data_ptr(), n, _ptr(talk), _ptr(sink),
+                                        float(scale), float(softcap), int(window), int(keep_first), int(chunk),
+                                        _ptr(value_rot), int(interleaved), H, G, dk, dv, v_row, int(value_div), bs,
+                                        int(splits), _ptr(ws), DTYPE_ID[q.dtype], _stream())
     _lib.check_mixers(rc, "b200_mixed_prompt_attn")
 
 
@@ -559,12 +582,14 @@ def qknorm_rotary_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_no
                          interleaved: bool = True) -> None:
     """Per-head RMS norm of q (in place) and k (weights ``[dk]``, None: no norm), rotary positions over the first
     ``2 * len(freqs)`` dimensions of every head with angle ``pos * freqs[i]`` (``freqs`` float64 on the device), k and v
-    stored in the pools at ``slot_mapping``."""
+    stored in the pools at ``slot_mapping``.  ``v_pool`` may hold fewer heads than ``k_pool`` (several score maps over the
+    same values)."""
     _need_cuda(q, k, v, k_pool, v_pool, slot_mapping, tok_pos)
     nb, G, bs, dk = k_pool.shape
-    dv = v_pool.shape[3]
+    Gv, dv = v_pool.shape[1], v_pool.shape[3]
     n = q.shape[0]
-    if q.shape[1] != H * dk or k.shape != (n, G * dk) or v.shape != (n, G * dv):
+    if q.shape[1] != H * dk or k.shape != (n, G * dk) or v.shape != (n, Gv * dv) or v_pool.shape[0] != nb \
+            or v_pool.shape[2] != bs:
         raise ValueError("q / k / v do not match the pools")
     if slot_mapping.dtype != torch.int64 or tok_pos.dtype != torch.int32:
         raise TypeError("slot_mapping is int64, tok_pos int32")
@@ -576,10 +601,11 @@ def qknorm_rotary_append(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, q_no
         if freqs.dtype != torch.float64 or not freqs.is_contiguous() or not freqs.is_cuda:
             raise ValueError("freqs is a contiguous float64 tensor on the device")
         rot_dims = 2 * freqs.numel()
-    rc = _lib_().b200_qknorm_rotary_append(q.data_ptr(), _rows2(q), k.data_ptr(), _rows2(k), v.data_ptr(), _rows2(v),
-                                           _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(freqs), rot_dims, int(interleaved),
-                                           k_pool.data_ptr(), v_pool.data_ptr(), slot_mapping.data_ptr(),
-                                           tok_pos.data_ptr(), n, H, G, dk, dv, bs, nb, DTYPE_ID[k_pool.dtype], _stream())
+    rc = _lib_().b200_qknorm_rotary_append_ext(q.data_ptr(), _rows2(q), k.data_ptr(), _rows2(k), v.data_ptr(), _rows2(v),
+                                               _ptr(q_norm), _ptr(k_norm), float(eps), _ptr(freqs), rot_dims,
+                                               int(interleaved), k_pool.data_ptr(), v_pool.data_ptr(),
+                                               slot_mapping.data_ptr(), tok_pos.data_ptr(), n, H, G, Gv, dk, dv, bs, nb,
+                                               DTYPE_ID[k_pool.dtype], _stream())
     _lib.check_mixers(rc, "b200_qknorm_rotary_append")
 
 
@@ -748,4 +774,133 @@ def weighted_expert_combine(ys: torch.Tensor, where: torch.Tensor, ids: torch.Te
                                               weights.data_ptr(), x_self.data_ptr(), _ptr(shared), n, top, int(n_real),
                                               width, DTYPE_ID[ys.dtype], _stream())
     _lib.check_mixers(rc, "b200_weighted_expert_combine")
+    return out
+
+
+# ---- token shift, sigmoid-gated post-norm sublayers, a decoupled rotated key part (csrc/b200_gated_ops.cu) -----------
+@_timed
+def token_shift(x: torch.Tensor, mu: torch.Tensor, state: torch.Tensor, seqs: torch.Tensor, max_count: int,
+                want_cast: bool = False):
+    """``out[t] = x[t] + (x[t - 1] - x[t]) * mu`` per channel over each sequence's tokens, in ``mu``'s dtype; the row before
+    a portion comes from ``state`` fp32 ``[slots, width]`` (zero for a fresh sequence), which then receives the portion's
+    last row.  Returns ``(out, x rounded to that dtype or None)``."""
+    _need_cuda(x, mu, state, seqs)
+    _check_seqs(seqs)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2:
+        raise ValueError("x must be contiguous fp32 [rows, width]")
+    n, W = x.shape
+    if mu.numel() != W or not mu.is_contiguous():
+        raise ValueError("mu is contiguous [width]")
+    if state.dtype != torch.float32 or state.dim() != 2 or state.shape[1] != W or not state.is_contiguous():
+        raise ValueError("state is contiguous fp32 [slots, width]")
+    T = mu.dtype
+    out = torch.empty((n, W), dtype=T, device=x.device)
+    cast = torch.empty((n, W), dtype=T, device=x.device) if want_cast else None
+    rc = _lib_().b200_token_shift(out.data_ptr(), W, _ptr(cast), x.data_ptr(), mu.data_ptr(), state.data_ptr(),
+                                  seqs.data_ptr(), seqs.shape[0], int(max_count), W, DTYPE_ID[T], _stream())
+    _lib.check_mixers(rc, "b200_token_shift")
+    return out, cast
+
+
+@_timed
+def latent_rotary_append(q_rot: torch.Tensor, q_out: torch.Tensor, dkv: torch.Tensor, c_norm: torch.Tensor, eps: float,
+                         freqs: Optional[torch.Tensor], gain: float, pool: torch.Tensor, slot_mapping: torch.Tensor,
+                         tok_pos: torch.Tensor) -> None:
+    """``dkv [n, rank + dr]``: its first ``rank = len(c_norm)`` columns RMS-normed with ``c_norm`` and its last ``dr``
+    turned by the position go to one row of the one-head ``pool [blocks, 1, bs, rank + dr]``; ``q_out[n, h, :] =
+    turn(q_rot[n, h, :])`` for 3-D views ``[n, H, dr]`` with contiguous last dimensions that do not overlap.  Pairs
+    ``(2i, 2i + 1)``, ``i < len(freqs)``, are turned by ``pos * freqs[i]`` with cos and sin times ``gain``."""
+    _need_cuda(q_rot, q_out, dkv, c_norm, pool, slot_mapping, tok_pos)
+    n, H, dr = q_rot.shape
+    rank = c_norm.numel()
+    if q_out.shape != q_rot.shape or q_rot.stride(2) != 1 or q_out.stride(2) != 1:
+        raise ValueError("q_rot and q_out are [n, H, dr] views with contiguous last dimensions")
+    if dkv.shape != (n, rank + dr) or pool.dim() != 4 or pool.shape[1] != 1 or pool.shape[3] != rank + dr \
+            or not pool.is_contiguous():
+        raise ValueError("dkv is [n, rank + dr] and the pool [blocks, 1, block size, rank + dr]")
+    T = pool.dtype
+    if any(t.dtype != T for t in (q_rot, q_out, dkv, c_norm)):
+        raise TypeError("activations, norm weight and pool share one dtype")
+    if slot_mapping.dtype != torch.int64 or tok_pos.dtype != torch.int32:
+        raise TypeError("slot_mapping is int64, tok_pos int32")
+    rot_dims = 0
+    if freqs is not None:
+        if freqs.dtype != torch.float64 or not freqs.is_contiguous() or not freqs.is_cuda:
+            raise ValueError("freqs is a contiguous float64 tensor on the device")
+        rot_dims = 2 * freqs.numel()
+    rc = _lib_().b200_latent_rotary_append(q_rot.data_ptr(), q_rot.stride(0), q_rot.stride(1), q_out.data_ptr(),
+                                           q_out.stride(0), q_out.stride(1), dkv.data_ptr(), _rows2(dkv), c_norm.data_ptr(),
+                                           float(eps), _ptr(freqs), float(gain), rot_dims, pool.data_ptr(),
+                                           slot_mapping.data_ptr(), tok_pos.data_ptr(), n, H, dr, rank, DTYPE_ID[T],
+                                           _stream())
+    _lib.check_mixers(rc, "b200_latent_rotary_append")
+
+
+@_timed
+def head_diff_norm(a: torch.Tensor, lam: float, out_scale: float, eps: float, rep: int, out: Optional[torch.Tensor] = None
+                   ) -> torch.Tensor:
+    """``a [n, 2H, dv]`` (a view with a contiguous last dimension) holds two score maps' outputs per head, map 1 of head
+    ``h`` at ``(h // rep) * 2 rep + h % rep`` and map 2 ``rep`` heads further: returns ``[n, H * dv]`` =
+    ``unit_rms(a1 - lam a2) * out_scale`` per head."""
+    _need_cuda(a)
+    n, H2, dv = a.shape
+    if a.stride(2) != 1 or H2 % (2 * rep):
+        raise ValueError("a is [n, 2H, dv] with a contiguous last dimension, H a multiple of rep")
+    H = H2 // 2
+    if out is None:
+        out = torch.empty((n, H * dv), dtype=a.dtype, device=a.device)
+    rc = _lib_().b200_head_diff_norm(out.data_ptr(), _rows2(out), a.data_ptr(), a.stride(0), a.stride(1), float(lam),
+                                     float(out_scale), float(eps), n, H, int(rep), dv, DTYPE_ID[a.dtype], _stream())
+    _lib.check_mixers(rc, "b200_head_diff_norm")
+    return out
+
+
+@_timed
+def gated_postnorm_residual(x: torch.Tensor, a: torch.Tensor, gate: Optional[torch.Tensor], w_norm: torch.Tensor,
+                            weight_offset: float, eps: float, want_copy: bool = True) -> Optional[torch.Tensor]:
+    """In place ``x += (weight_offset + w_norm) * y * rsqrt(mean(y^2) + eps)`` with ``y = a * sigmoid(gate)`` on the fp32
+    residual; ``a`` is fp32 or of the weights' dtype, ``gate`` (logits, optional) of the weights' dtype.  With
+    ``want_copy`` returns the new ``x`` in the weights' dtype."""
+    _need_cuda(x, a, w_norm)
+    if x.dtype != torch.float32 or not x.is_contiguous() or x.dim() != 2 or a.shape != x.shape:
+        raise ValueError("x must be contiguous fp32 [rows, width] and the branch of the same shape")
+    T = w_norm.dtype
+    if a.dtype not in (T, torch.float32) or (gate is not None and (gate.dtype != T or gate.shape != x.shape)):
+        raise TypeError("a is fp32 or of the weights' dtype, the gate of the weights' dtype")
+    out = torch.empty(x.shape, dtype=T, device=x.device) if want_copy else None
+    rc = _lib_().b200_gated_postnorm_residual(x.data_ptr(), a.data_ptr(), _rows2(a),
+                                              int(a.dtype == torch.float32 and T != torch.float32), _ptr(gate),
+                                              _rows2(gate) if gate is not None else 0, w_norm.data_ptr(),
+                                              float(weight_offset), _ptr(out), float(eps), x.shape[0], x.shape[1],
+                                              DTYPE_ID[T], _stream())
+    _lib.check_mixers(rc, "b200_gated_postnorm_residual")
+    return out
+
+
+@_timed
+def relu_squared(z: torch.Tensor) -> torch.Tensor:
+    """``max(z, 0)^2`` of 2-D rows (a column slice is fine), contiguous out."""
+    _need_cuda(z)
+    out = torch.empty(z.shape, dtype=z.dtype, device=z.device)
+    if z.shape[0]:
+        rc = _lib_().b200_relu_squared(out.data_ptr(), z.data_ptr(), _rows2(z), z.shape[0], z.shape[1], DTYPE_ID[z.dtype],
+                                       _stream())
+        _lib.check_mixers(rc, "b200_relu_squared")
+    return out
+
+
+@_timed
+def gated_table_rows(z: torch.Tensor, table: torch.Tensor, col0: int, tokens: torch.Tensor) -> torch.Tensor:
+    """``gelu_tanh(z[n, c]) * table[tokens[n], col0 + c]``: ``z [n, d]``, ``table [rows, >= col0 + d]`` of the same dtype,
+    ``tokens`` int64 ``[n]``."""
+    _need_cuda(z, table, tokens)
+    n, d = z.shape
+    if table.dtype != z.dtype or table.dim() != 2 or table.stride(1) != 1 or col0 + d > table.shape[1]:
+        raise ValueError("the table is 2-D in z's dtype with at least col0 + d columns")
+    if tokens.dtype != torch.int64 or tokens.numel() != n or not tokens.is_contiguous():
+        raise ValueError("tokens is contiguous int64 [n]")
+    out = torch.empty((n, d), dtype=z.dtype, device=z.device)
+    rc = _lib_().b200_gated_table_rows(out.data_ptr(), z.data_ptr(), _rows2(z), table.data_ptr(), table.stride(0), int(col0),
+                                       tokens.data_ptr(), n, d, DTYPE_ID[z.dtype], _stream())
+    _lib.check_mixers(rc, "b200_gated_table_rows")
     return out

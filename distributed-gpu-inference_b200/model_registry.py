@@ -69,7 +69,7 @@ def _register_builtin() -> None:
     if _builtin_done:
         return
     _builtin_done = True
-    from . import fibirax_layer, petipel_layer, sanesun_layer
+    from . import fibirax_layer, petipel_layer, sanesun_layer, vatazen_layer
     from .testing import LlamaShapeConfig, build_product_shards
 
     def llama_config(raw: Dict[str, Any]):
@@ -81,3 +81,4 @@ def _register_builtin() -> None:
     register(Architecture("Petipel", petipel_layer.PetipelConfig.from_dict, petipel_layer.build_shards, "ragged"))
     register(Architecture("Sanesun", sanesun_layer.SanesunConfig.from_dict, sanesun_layer.build_shards, "ragged"))
     register(Architecture("Fibirax", fibirax_layer.FibiraxConfig.from_dict, fibirax_layer.build_shards, "ragged"))
+    register(Architecture("Vatazen", vatazen_layer.VatazenConfig.from_dict, vatazen_layer.build_shards, "ragged"))

@@ -191,6 +191,7 @@ class RaggedBatchState:
     v_first        values the first value-mixing attention layer stored for this step's tokens (set by that layer)
     pending_norm   the next sublayer's normed input when the previous layer already computed it in its epilogue
     scan_host      the rows of ``scan_seqs`` as a host list (what ``scan_plan`` cuts long portions from)
+    token_ids      int64 [N]              the step's token ids (layers that read a token table of their own)
     """
 
     tok_pos: torch.Tensor
@@ -203,6 +204,11 @@ class RaggedBatchState:
     pending_norm: Optional[torch.Tensor] = None
     _tiles: Optional[dict] = None
     scan_host: Optional[list] = None
+    token_ids: Optional[torch.Tensor] = None
+
+    def max_count(self) -> int:
+        """Tokens of the step's longest portion."""
+        return max(count for _first, count, _row, _past in self.spans)
 
     def max_context(self) -> int:
         """Tokens of the longest sequence of the step, this step's included."""

@@ -211,6 +211,7 @@ class RaggedStepEngine:
             scan_host=scans,
         )
         h = up(np.asarray(ids, dtype=np.int64))
+        st.token_ids = h
         for si, shard in enumerate(self.shards):
             handles = []
             for kv_j, st_j in self._layer_slot[si]:

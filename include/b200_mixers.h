@@ -158,6 +158,19 @@ int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_st
                           float softcap, int window, int keep_first, int unrotate, int interleaved, float rot_base, int H,
                           int G, int dk, int dv, int block_size, int dtype, void* stream);
 
+/* The same with three more parameters.  chunk > 0: a position also sees only keys j with j / chunk == i / chunk (blocks
+ * counted from position 0 of the sequence).  v_row: elements between value rows of v_pool, so that the values may be the
+ * first dv columns of wider rows (v_pool == k_pool with one kv head: a latent row serves as key over its whole width dk
+ * and as value over its first dv columns).  v_div: value head = key head / v_div; v_pool holds G / v_div heads per block
+ * (several score maps over the same values). */
+int b200_mixed_paged_attn_ext(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q,
+                              int64_t q_tok_stride, int64_t q_head_stride, const void* gate, int64_t gate_stride,
+                              const void* k_pool, const void* v_pool, const int32_t* block_tables, int table_stride,
+                              const int32_t* tok_row, const int32_t* tok_pos, int n_tok, const float* talk,
+                              const float* sink, float scale, float softcap, int window, int keep_first, int chunk,
+                              int unrotate, int interleaved, float rot_base, int H, int G, int dk, int dv, int v_row,
+                              int v_div, int block_size, int dtype, void* stream);
+
 /* The same attention on the tensor cores (16-bit T; dk a multiple of 16, dv a multiple of 8 up to 256, and a shared-
  * memory budget that b200_mixed_prompt_attn_supported checks; same_pool: keys and values are one pool).  tiles: int32
  * [n_tiles, 3] = (first packed row, token count <= 16, block-table row); a tile's tokens are consecutive positions of
@@ -179,6 +192,15 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
                            float scale, float softcap, int window, int keep_first, const float* value_rot, int interleaved,
                            int H, int G, int dk, int dv, int block_size, int n_splits, float* workspace, int dtype,
                            void* stream);
+
+/* b200_mixed_prompt_attn with chunk, v_row and v_div as in b200_mixed_paged_attn_ext (v_row a multiple of 8). */
+int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q,
+                               int64_t q_tok_stride, int64_t q_head_stride, const void* gate, int64_t gate_stride,
+                               const void* k_pool, const void* v_pool, const int32_t* block_tables, int table_stride,
+                               const int32_t* tiles, int n_tiles, const int32_t* tok_pos, int n_tok, const float* talk,
+                               const float* sink, float scale, float softcap, int window, int keep_first, int chunk,
+                               const float* value_rot, int interleaved, int H, int G, int dk, int dv, int v_row, int v_div,
+                               int block_size, int n_splits, float* workspace, int dtype, void* stream);
 
 /* out[t, c] = silu(sum_i w[c][i] * x[t - (taps - 1 - i), c]) per sequence (SeqSpan rows); inputs before the portion
  * come from tail [slots, taps - 1, C] (fp32, oldest first), which then receives the portion's last taps - 1 inputs. */
@@ -212,6 +234,14 @@ int b200_qknorm_rotary_append(void* q, int64_t q_stride, const void* k, int64_t 
                               int interleaved, void* k_pool, void* v_pool, const int64_t* slot_mapping,
                               const int32_t* tok_pos, int n_tok, int H, int G, int dk, int dv, int block_size,
                               int64_t max_blocks, int dtype, void* stream);
+
+/* The same with Gv value heads in v [n_tok, Gv*dv] and v_pool [max_blocks, Gv, block_size, dv] (layouts whose key heads
+ * outnumber the value heads: several score maps over the same values). */
+int b200_qknorm_rotary_append_ext(void* q, int64_t q_stride, const void* k, int64_t k_stride, const void* v,
+                                  int64_t v_stride, const void* q_norm, const void* k_norm, float eps, const double* freqs,
+                                  int rot_dims, int interleaved, void* k_pool, void* v_pool, const int64_t* slot_mapping,
+                                  const int32_t* tok_pos, int n_tok, int H, int G, int Gv, int dk, int dv, int block_size,
+                                  int64_t max_blocks, int dtype, void* stream);
 
 /* Retention per (sequence, head) over the sequence's tokens of this step, in order (SeqSpan rows as above):
  *   S <- decay[h] S + (k_scale k_t) v_t^T;   o_t = S^T q_t
@@ -264,6 +294,47 @@ int b200_gather_rows(void* xs, const void* h, const int64_t* src, int64_t n_rows
 int b200_weighted_expert_combine(float* out, const void* ys, const int64_t* where, const int32_t* ids, const float* weights,
                                  const float* x_self, const void* shared_rows, int64_t n_tok, int top, int n_real,
                                  int width, int dtype, void* stream);
+
+/* ---- pieces for designs with token shift, sigmoid-gated post-norm sublayers, a decoupled rotated key part --------- */
+
+/* out[t] = T(x[t] + (x[t - 1] - x[t]) * mu) per channel over each sequence's tokens (SeqSpan rows); the row before a
+ * portion's first token comes from state [slots, width] (fp32; zero when the sequence is fresh), which then receives the
+ * portion's last row.  x fp32 [n_tok, width] contiguous; out T rows with stride out_stride; x_cast (may be NULL) T
+ * [n_tok, width] receives the unshifted rows rounded to T.  max_count: the largest token count among seqs. */
+int b200_token_shift(void* out, int64_t out_stride, void* x_cast, const float* x, const void* mu, float* state,
+                     const int32_t* seqs, int n_seqs, int max_count, int width, int dtype, void* stream);
+
+/* Latent attention with a decoupled rotated key part.  dkv rows (T, stride dkv_stride) hold rank + rot_width columns:
+ * pool[slot] = [rms_norm(dkv[:rank]; c_norm) | turn(dkv[rank:])] (a one-head pool of rows rank + rot_width; negative slot =
+ * skip), and q_out[n, h, :] = turn(q_rot[n, h, :]) for the rot_width rotated columns of every query head (element (n, h, i)
+ * at n * tok_stride + h * head_stride + i; q_out must not overlap q_rot).  turn: pairs (2i, 2i + 1), i < rot_dims / 2, go to
+ * (u c - v s, v c + u s) with c, s = gain * cos, sin(pos * freqs[i]); columns from rot_dims on pass unchanged.  freqs:
+ * rot_dims / 2 doubles ON THE DEVICE. */
+int b200_latent_rotary_append(const void* q_rot, int64_t q_tok_stride, int64_t q_head_stride, void* q_out,
+                              int64_t qo_tok_stride, int64_t qo_head_stride, const void* dkv, int64_t dkv_stride,
+                              const void* c_norm, float eps, const double* freqs, float gain, int rot_dims, void* pool,
+                              const int64_t* slot_mapping, const int32_t* tok_pos, int n_tok, int H, int rot_width,
+                              int rank, int dtype, void* stream);
+
+/* Two score maps per head over the same values: with a1, a2 = a[n, (h / rep) * 2 rep + (h % rep) (+ rep), :],
+ * out[n, h * dv + i] = o_i * rsqrt(mean_i o^2 + eps) * out_scale, o = a1 - lam * a2.  a: T, element (n, head, i) at
+ * n * a_tok_stride + head * a_head_stride + i; out T rows with stride out_stride. */
+int b200_head_diff_norm(void* out, int64_t out_stride, const void* a, int64_t a_tok_stride, int64_t a_head_stride, float lam,
+                        float out_scale, float eps, int64_t n_tok, int H, int rep, int dv, int dtype, void* stream);
+
+/* y = a * sigmoid(gate) (gate T rows, may be NULL);  x += (weight_offset + w_norm) * y * rsqrt(mean(y^2) + eps)  in place
+ * on the fp32 residual; x_out (T, may be NULL) receives the new x.  a is fp32 (a_is_f32) or T. */
+int b200_gated_postnorm_residual(float* x, const void* a, int64_t a_stride, int a_is_f32, const void* gate,
+                                 int64_t gate_stride, const void* w_norm, float weight_offset, void* x_out, float eps,
+                                 int rows, int width, int dtype, void* stream);
+
+/* out[r, c] = max(z[r, c], 0)^2; z rows with stride z_stride, out contiguous [rows, ff]. */
+int b200_relu_squared(void* out, const void* z, int64_t z_stride, int64_t rows, int ff, int dtype, void* stream);
+
+/* out[n, c] = gelu_tanh(z[n, c]) * table[tokens[n]][col0 + c], c < d; gelu_tanh(z) = z/2 (1 + tanh(sqrt(2/pi) (z +
+ * 0.044715 z^3))).  table T rows with stride table_stride, tokens int64. */
+int b200_gated_table_rows(void* out, const void* z, int64_t z_stride, const void* table, int64_t table_stride, int col0,
+                          const int64_t* tokens, int64_t n_tok, int d, int dtype, void* stream);
 
 #ifdef __cplusplus
 }
