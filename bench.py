@@ -679,10 +679,11 @@ def main():
     ap.add_argument("--no-parity", action="store_true", help="multi-GPU: skip the token checks of the run")
     ap.add_argument("--no-vocab-parallel-head", action="store_true",
                     help="multi-GPU: keep lm_head + argmax on the last stage (instead of the vocabulary-parallel head)")
-    ap.add_argument("--compare", default="", choices=["", "petipel", "sanesun", "fibirax"],
+    ap.add_argument("--compare", default="", choices=["", "petipel", "sanesun", "fibirax", "vatazen"],
                     help="petipel: prompt-pass and decode throughput of the Petipel model class (ragged step engine) beside "
                          "a Llama shape of equal size, with per-kernel times; sanesun: the Sanesun model class beside a "
                          "Petipel model of equal size; fibirax: the Fibirax model class beside a Petipel model of equal size; "
+                         "vatazen: the Vatazen model class beside a Fibirax model of equal size; "
                          "each prints its own JSON line")
     ap.add_argument("--compare-sizes", default="", help="with --compare: comma-separated subset of w1024,w2048,w4096")
     args = ap.parse_args()
@@ -695,6 +696,11 @@ def main():
         from dgi_b200.bench_ragged import run_fibirax
 
         run_fibirax(args, measured_peaks, ClockSampler)
+        return
+    if args.compare == "vatazen":
+        from dgi_b200.bench_ragged import run_vatazen
+
+        run_vatazen(args, measured_peaks, ClockSampler)
         return
     if args.compare == "sanesun":
         from dgi_b200.bench_ragged import run_sanesun

@@ -13,6 +13,11 @@ on the same engine), with every kernel of both against its floor so that like ke
 ``bench.py --compare fibirax``: the same two steps for the Fibirax model class (a windowed attention AND a retention in
 every layer, routed experts in every layer) beside a Petipel model of equal width, depth, head layout and expert sizes
 whose layers alternate attention and recurrence, again with every kernel of both against its floor.
+
+``bench.py --compare vatazen``: the same two steps for the Vatazen model class (latent layers with a decoupled rotated
+key part and differential layers in turn, routed experts in every layer) beside a Fibirax model of equal width, depth,
+head layout and expert sizes (its closest relative here: post-norm sublayers that read the residual itself, windowed sink
+attention on the same tensor-core kernel, softmax routing over the same dispatch).
 """
 from __future__ import annotations
 
@@ -459,6 +464,140 @@ def _fibirax_kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx, hbm, tf) -> D
             "clamped_glu": (n_tok * (top + 1) // 2 * s["eff"] * 6, 0),
             "gather_rows": (n_tok * top * W * 4, 0),
             "weighted_expert_combine": (n_tok * top * W * 2 + n_tok * W * (4 + 4 + 2), 0),
+        }
+        for name, ts in by.items():
+            t = statistics.mean(ts)
+            entry = {"us": round(t * 1e6, 1), "calls": len(ts)}
+            if name in floors:
+                nbytes, flops = floors[name]
+                floor = max(nbytes / hbm, flops / tf)
+                entry["of_floor"] = round(floor / t, 3)
+                entry["bound"] = "math" if flops / tf > nbytes / hbm else "memory"
+            out.setdefault(phase, {})[name] = entry
+    return out
+
+
+# ---- Vatazen beside Fibirax ------------------------------------------------------------------------------------------
+VATAZEN_WINDOW = 512      # the latent layers' window; the differential layers see blocks of this many positions too
+VATAZEN_RANK, VATAZEN_ROT, VATAZEN_SIDE = 256, 64, 64
+
+
+def vatazen_config(s: Dict[str, int]) -> Dict[str, Any]:
+    """Latent and differential layers in turn.  A differential layer runs two maps per head, so it gets half the heads of
+    the size's head layout: both layer types then put ``heads`` score maps on the attention kernel."""
+    lat = {"heads": s["heads"], "dim": s["dk"], "rot_dim": VATAZEN_ROT, "vdim": s["dv"], "kv_rank": VATAZEN_RANK,
+           "scale": 1.0 / math.sqrt(s["dk"] + VATAZEN_ROT), "mask": {"size": VATAZEN_WINDOW},
+           "rot": {"base": 10000.0, "dims": VATAZEN_ROT,
+                   "scaling": {"factor": 8.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}
+    dif = {"heads": s["heads"] // 2, "kv_heads": max(s["kv"] // 2, 1), "dim": s["dk"], "vdim": s["dv"], "diff": 0.3,
+           "scale": 1.0 / math.sqrt(s["dk"]), "mask": {"size": VATAZEN_WINDOW}}
+    mlp = {"kind": "moe", "expert": {"ff": s["eff"]}, "router": {"experts": s["experts"], "top": s["top"]}}
+    layers = [{"type": "latent_attention" if i % 2 == 0 else "attention", "mixer": lat if i % 2 == 0 else dif, "mlp": mlp}
+              for i in range(LAYERS)]
+    return {"architecture": "Vatazen", "width": s["width"], "vocab": VOCAB, "embedding": {"scale": 1.0},
+            "norm": {"eps": 1e-6}, "token_side": {"dim": VATAZEN_SIDE}, "layers": layers}
+
+
+def run_vatazen(args, measured_peaks, ClockSampler) -> None:
+    from . import fibirax_layer as Fx
+    from . import mixer_ops
+    from . import vatazen_layer as Vz
+    from .ragged_engine import RaggedStepEngine
+
+    dev = "cuda:0"
+    peaks, how = measured_peaks()
+    hbm, tf = peaks["hbm_gbs"] * 1e9, peaks["bf16_tflops"] * 1e12
+    steps, warmup = max(3, args.steps), max(3, args.warmup)
+    B, Pn, ctx, Bd = 8, 2048, 2048, 64
+    g = torch.Generator().manual_seed(0)
+    sampler = ClockSampler(0)
+    sampler.start()
+    report: Dict[str, Any] = {}
+    for name, s in SIZES.items():
+        if args.compare_sizes and name not in args.compare_sizes.split(","):
+            continue
+        row: Dict[str, Any] = {}
+        prompts = torch.randint(0, VOCAB, (Bd, ctx), generator=g).tolist()
+        for label, mod, raw in (("vatazen", Vz, vatazen_config(s)), ("fibirax", Fx, fibirax_config(s))):
+            cfg = (Vz.VatazenConfig if mod is Vz else Fx.FibiraxConfig).from_dict(raw)
+            shards = mod.build_shards(cfg, mod.random_checkpoint(cfg, seed=0), [(0, LAYERS)], dev, torch.bfloat16)
+            eng = RaggedStepEngine(shards, max_tokens=Bd * (ctx + 64), max_seqs=Bd, fp32_logits=False)
+
+            def prompt_step():
+                eng.step([(i, prompts[i][:Pn], [Pn - 1]) for i in range(B)])
+                for i in range(B):
+                    eng.finish(i)
+
+            ms = _time_steps(prompt_step, steps, warmup)
+            row[label + "_prefill_tok_s"] = round(B * Pn / ms * 1e3)
+            mixer_ops.EVENTS = []
+            prompt_step()
+            torch.cuda.synchronize()
+            ev_prompt, mixer_ops.EVENTS = mixer_ops.EVENTS, None
+            for i in range(0, Bd, B):
+                eng.step([(j, prompts[j], []) for j in range(i, i + B)])
+            nxt = [[1] for _ in range(Bd)]
+
+            def decode_step():
+                eng.step([(j, nxt[j], [0]) for j in range(Bd)])
+
+            n_dec = min(steps, 32)
+            ms = _time_steps(decode_step, n_dec, warmup)
+            row[label + "_decode_tok_s"] = round(Bd / ms * 1e3)
+            mixer_ops.EVENTS = []
+            decode_step()
+            torch.cuda.synchronize()
+            ev_decode, mixer_ops.EVENTS = mixer_ops.EVENTS, None
+            eng.release()
+            table = _vatazen_kernel_table if mod is Vz else _fibirax_kernel_table
+            row[label + "_kernels"] = table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx + warmup + n_dec, hbm, tf)
+            del eng, shards
+            torch.cuda.empty_cache()
+        row["inputs_exceed_l2"] = bool(Bd * ctx * (VATAZEN_RANK + VATAZEN_ROT) * 2 * LAYERS > 126e6)
+        report[name] = row
+    clocks = sampler.stop()
+    print(json.dumps({"bench": "vatazen_vs_fibirax", "unit": "tokens/s", "dtype": "bf16", "data": "synthetic",
+                      "layers": LAYERS, "prompt_step": f"{B} x {Pn} tokens", "decode_step": f"{Bd} sequences at {ctx}",
+                      "peaks": how, "sizes": report, "clocks": clocks}), flush=True)
+
+
+def _vatazen_kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx, hbm, tf) -> Dict[str, Any]:
+    """Like ``_kernel_table`` for the Vatazen kernels.  The attention kernel serves latent and differential layers in
+    turn; its calls are listed per layer type (even calls of a step are latent layers)."""
+    out: Dict[str, Any] = {}
+    W, H, G, dk, dv, top = s["width"], s["heads"], s["kv"], s["dk"], s["dv"], s["top"]
+    r, dr = VATAZEN_RANK, VATAZEN_ROT
+    Hd, Gd = H // 2, max(G // 2, 1)
+    for phase, events, n_tok, past in (("prompt", ev_prompt, B * Pn, 0), ("decode", ev_decode, Bd, ctx)):
+        by: Dict[str, List[float]] = {}
+        n_attn = 0
+        for name, a, b in events:
+            if name in ("mixed_prompt_attention", "mixed_paged_attention"):
+                name += "[latent]" if n_attn % 2 == 0 else "[differential]"
+                n_attn += 1
+            by.setdefault(name, []).append(a.elapsed_time(b) * 1e-3)
+        per_seq = n_tok // (B if phase == "prompt" else Bd)
+        n_seq = n_tok // per_seq
+        pairs_win = sum(min(past + t + 1, VATAZEN_WINDOW) for t in range(per_seq))
+        pairs_blk = sum((past + t) % VATAZEN_WINDOW + 1 for t in range(per_seq))
+        keys_win = min(past + per_seq, VATAZEN_WINDOW + per_seq)
+        keys_blk = min(past + per_seq, (past % VATAZEN_WINDOW) + per_seq)
+        lat = (n_seq * keys_win * (r + dr) * 2 + n_tok * H * (2 * r + dr) * 2, n_seq * H * 2 * (2 * r + dr) * pairs_win)
+        dif = (n_seq * keys_blk * Gd * (2 * dk + dv) * 2 + n_tok * 2 * Hd * (dk + dv) * 2, n_seq * 2 * Hd * 2 * (dk + dv) * pairs_blk)
+        floors = {
+            "token_shift": (n_tok * W * 7, 0),
+            "latent_rotary_append": (n_tok * (H * dr + r + dr) * 4, 0),
+            "qknorm_rotary_append": (n_tok * (2 * Hd * dk * 2 + Gd * (2 * dk + dv) * 2) * 2, 0),
+            "mixed_prompt_attention[latent]": lat,
+            "mixed_paged_attention[latent]": lat,
+            "mixed_prompt_attention[differential]": dif,
+            "mixed_paged_attention[differential]": dif,
+            "head_diff_norm": (n_tok * Hd * dv * 6, 0),
+            "gated_postnorm_residual": (n_tok * W * 14, 0),
+            "relu_squared": (n_tok * top * s["eff"] * 4, 0),
+            "gated_table_rows": (n_tok * VATAZEN_SIDE * 6, 0),
+            "gather_rows": (n_tok * top * W * 4, 0),
+            "weighted_expert_combine": (n_tok * top * W * 2 + n_tok * W * (4 + 4), 0),
         }
         for name, ts in by.items():
             t = statistics.mean(ts)

@@ -262,6 +262,8 @@ struct AttnArgs {
   int chunk = 0;   // > 0: a position sees only the keys of its own block of `chunk` positions (counted from 0)
   int v_row = 0;   // elements between value rows in v_pool (the value size unless the values are the first columns of wider rows)
   int v_div = 1;   // value head = key head / v_div (several key heads read one value head)
+  int row_heads = 0;   // tensor-core kernel, > 0: a tile is ONE token and its 16 rows are consecutive heads of `row_heads`
+                       // that share one kv head; H then counts groups of 16 heads
 };
 
 // first key a position sees (the kept first tokens of a window aside)
@@ -519,7 +521,9 @@ constexpr int kTcKeys = 32;
 constexpr int kTcRows = 16;
 constexpr int kTcRawStride = 40;
 
-template <typename T, int DV8, int HW>
+// EXT: the kernel also knows blocks of positions, values inside wider rows or shared by several key heads, and heads on
+// the rows; layers without any of these run the instantiation that carries none of it.
+template <typename T, int DV8, int HW, bool EXT>
 __global__ void __launch_bounds__(kTcWarps * 32, (HW == 1 && DV8 <= 16) ? 2 : 1)
 mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, const float* __restrict__ rot_tab,
                          float* __restrict__ ws, int n_tok, int stages) {
@@ -535,18 +539,42 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
   const int Gs = (mixed ? G - 1 : min(H - 1, h0 + HC - 1) / rep) - g_lo + 1;   // kv heads staged per tile
   const T* kp = static_cast<const T*>(A.k_pool);
   const T* vp = static_cast<const T*>(A.v_pool);
-  const bool alias = (A.v_pool == A.k_pool) && A.v_div == 1 && DVP <= dk;   // the values are the first columns of the staged key rows
+  const int v_div = EXT ? A.v_div : 1, v_row = EXT ? A.v_row : dv;
+  const bool alias = (A.v_pool == A.k_pool) && v_div == 1 && DVP <= dk;   // the values are the first columns of the staged key rows
   const int ks = dk + 8, vs = alias ? ks : DVP + 8;                             // row strides in elements
-  const int Gv = G / A.v_div;
+  const int Gv = G / v_div;
+  auto first_seen = [&](int p) {     // first key a position sees (the kept first tokens of a window aside)
+    int lo = A.window > 0 ? max(0, p - A.window + 1) : 0;
+    if (EXT && A.chunk > 0) lo = max(lo, (p / A.chunk) * A.chunk);
+    return lo;
+  };
   const int stage_elems = Gs * kTcKeys * (ks + (alias ? 0 : vs));                 // one stage: K rows, then V rows
   T* stage0 = reinterpret_cast<T*>(tc_smem);
   const T* Ks = stage0;                                                         // the stage being computed on
   const T* Vs = alias ? stage0 : stage0 + Gs * kTcKeys * ks;
   float* raw = reinterpret_cast<float*>(stage0 + stages * stage_elems);         // [H][16][40]
   float* talk_s = raw + (mixed ? H * kTcRows * kTcRawStride : 0);                               // [HC][H]
-  const int p0 = A.tok_pos[row0], p_last = p0 + cnt - 1;
+  const int RH = EXT ? A.row_heads : 0;
+  // heads on the rows: a warp's 16 query rows are staged once (a lone warp per CTA cannot hide their global latency)
+  T* q_s = reinterpret_cast<T*>(talk_s + (mixed ? HC * H : 0));                                 // [HC][16][dk + 8]
+  if (RH) {
+    const int kch = dk / 8;
+    for (int hl = warp * HW; hl < warp * HW + HW; ++hl) {
+      const int h = h0 + hl;
+      if (h >= H) continue;
+      for (int e = lane; e < kTcRows * kch; e += 32) {
+        const int r = e / kch, ch = e - r * kch;
+        int4 v = make_int4(0, 0, 0, 0);
+        if (16 * h + r < RH)
+          v = *reinterpret_cast<const int4*>(static_cast<const T*>(A.q) + static_cast<int64_t>(row0) * A.q_tok_stride +
+                                             (16 * h + r) * A.q_head_stride + ch * 8);
+        *reinterpret_cast<int4*>(q_s + (hl * kTcRows + r) * ks + ch * 8) = v;
+      }
+    }
+  }
+  const int p0 = A.tok_pos[row0], p_last = RH ? p0 : p0 + cnt - 1;
   const int32_t* table = A.block_tables + static_cast<int64_t>(trow) * A.table_stride;
-  const int lo0 = first_visible(A, p0);
+  const int lo0 = first_seen(p0);
   const int kf = A.window > 0 ? min(A.keep_first, lo0) : 0;
   const int nA = (kf + kTcKeys - 1) / kTcKeys;
   const int cB0 = max(nA, lo0 / kTcKeys), cB1 = p_last / kTcKeys;
@@ -576,9 +604,12 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
   auto scores = [&](int h, float (&s)[4][4]) {
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-    const T* qa = qbase + static_cast<int64_t>(row0 + qr) * A.q_tok_stride + h * A.q_head_stride + qc;
-    const T* qb = qa + 8 * A.q_tok_stride;
-    const bool va = qr < cnt, vb = qr + 8 < cnt;
+    // heads on the rows: the staged rows (rows past the heads are zero); else the query rows in global memory
+    const T* qa = RH ? q_s + ((h - h0) * kTcRows + qr) * ks + qc
+                     : qbase + static_cast<int64_t>(row0 + qr) * A.q_tok_stride + h * A.q_head_stride + qc;
+    const T* qb = qa + 8 * (RH ? static_cast<int64_t>(ks) : A.q_tok_stride);
+    const int rows = RH ? min(16, RH - 16 * h) : cnt;
+    const bool va = qr < rows, vb = qr + 8 < rows;
     const T* kt = Ks + (h / rep - g_lo) * kTcKeys * ks + qr * ks + qc;
     for (int kk = 0; kk < dk; kk += 16) {
       uint32_t a[4];
@@ -615,7 +646,7 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
       for (int e = threadIdx.x; e < Gs * kTcKeys * vch; e += blockDim.x) {
         const int ch = e % vch, r = e / vch, key = r % kTcKeys, gi = r / kTcKeys, j = j0 + key;
         const bool ok = j <= p_last;
-        const T* src = ok ? vp + (static_cast<int64_t>(table[j / bs] * Gv + (g_lo + gi) / A.v_div) * bs + j % bs) * A.v_row + ch * 8 : vp;
+        const T* src = ok ? vp + (static_cast<int64_t>(table[j / bs] * Gv + (g_lo + gi) / v_div) * bs + j % bs) * v_row + ch * 8 : vp;
         stage16(Vd + r * vs + ch * 8, src, ok);
       }
     }
@@ -677,9 +708,9 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
       }
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int row = qr + 8 * half, p = p0 + row;
-        const bool row_ok = row < cnt;
-        const int lo_p = first_visible(A, p);
+        const int row = qr + 8 * half, p = RH ? p0 : p0 + row;
+        const bool row_ok = row < (RH ? min(16, RH - 16 * h) : cnt);
+        const int lo_p = first_seen(p);
         float mx = -INFINITY;
 #pragma unroll
         for (int nt = 0; nt < 4; ++nt)
@@ -748,8 +779,9 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int row = qr + 8 * half;
-        if (row >= cnt) continue;
-        float* dst = ws + ((static_cast<int64_t>(blockIdx.z) * n_tok + row0 + row) * H + h) * (DVP + 2);
+        if (row >= (RH ? min(16, RH - 16 * h) : cnt)) continue;
+        float* dst = RH ? ws + ((static_cast<int64_t>(blockIdx.z) * n_tok + row0) * RH + 16 * h + row) * (DVP + 2)
+                        : ws + ((static_cast<int64_t>(blockIdx.z) * n_tok + row0 + row) * H + h) * (DVP + 2);
         if (qc == 0) {
           dst[0] = m_r[hw][half];
           dst[1] = l_r[hw][half];
@@ -773,10 +805,10 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
     for (int half = 0; half < 2; ++half) {
       const int row = qr + 8 * half;
       float f = 0.f;
-      if (row < cnt) {
+      if (row < (RH ? min(16, RH - 16 * h) : cnt)) {
         float m = m_r[hw][half], l = l_r[hw][half];
         if (A.sink) {
-          const float sk = A.sink[h], M = fmaxf(m, sk);
+          const float sk = A.sink[RH ? 16 * h + row : h], M = fmaxf(m, sk);
           l = l * expf(m - M) + expf(sk - M);
           f = expf(m - M) / l;
         } else {
@@ -794,8 +826,9 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
         const int row = qr + 8 * half;
-        if (row >= cnt) continue;
-        T* orow = outp + static_cast<int64_t>(row0 + row) * A.out_tok_stride + h * A.out_head_stride;
+        if (row >= (RH ? min(16, RH - 16 * h) : cnt)) continue;
+        T* orow = RH ? outp + static_cast<int64_t>(row0) * A.out_tok_stride + (16 * h + row) * A.out_head_stride
+                     : outp + static_cast<int64_t>(row0 + row) * A.out_tok_stride + h * A.out_head_stride;
 #pragma unroll
         for (int nt = 0; nt < DV8; ++nt) {
           const int c = nt * 8 + qc;
@@ -895,7 +928,8 @@ struct TcPlan {
   size_t smem;
 };
 
-inline bool tc_plan(int H, int G, int dk, int dv, bool has_talk, bool same_pool, bool unrotate, int dtype, TcPlan* plan) {
+inline bool tc_plan(int H, int G, int dk, int dv, bool has_talk, bool same_pool, bool unrotate, int dtype, TcPlan* plan,
+                    bool heads_as_rows = false) {
   if (dtype == B200_DTYPE_F32 || dk % 16 || dv % 8 || dv > 256 || H % G) return false;
   const int dv8 = dv <= 64 ? 8 : (dv <= 128 ? 16 : 32), dvp = dv8 * 8;
   // two heads per warp pay when the CTA's heads share what is staged: with a mixing matrix (all heads' raw scores are
@@ -908,6 +942,7 @@ inline bool tc_plan(int H, int G, int dk, int dv, bool has_talk, bool same_pool,
   if (!alias) stage += static_cast<size_t>(gs) * kTcKeys * (dvp + 8) * 2;
   size_t rest = 0;
   if (has_talk) rest = sizeof(float) * (static_cast<size_t>(H) * kTcRows * kTcRawStride + static_cast<size_t>(kTcWarps) * hw * H);
+  if (heads_as_rows) rest += static_cast<size_t>(kTcWarps) * hw * kTcRows * (dk + 8) * 2;   // the staged query rows
   const size_t slab = unrotate ? sizeof(float) * kTcWarps * kTcRows * static_cast<size_t>(dvp) : 0;
   const size_t cap = 227 * 1024;
   int stages = 2;
@@ -1359,7 +1394,7 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
                            void* stream) {
   return b200_mixed_prompt_attn_ext(out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride,
                                     k_pool, v_pool, block_tables, table_stride, tiles, n_tiles, tok_pos, n_tok, talk, sink,
-                                    scale, softcap, window, keep_first, 0, value_rot, interleaved, H, G, dk, dv, dv, 1,
+                                    scale, softcap, window, keep_first, 0, value_rot, interleaved, H, G, dk, dv, dv, 1, 0,
                                     block_size, n_splits, workspace, dtype, stream);
 }
 
@@ -1369,9 +1404,15 @@ int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_he
                                const int32_t* tiles, int n_tiles, const int32_t* tok_pos, int n_tok, const float* talk,
                                const float* sink, float scale, float softcap, int window, int keep_first, int chunk,
                                const float* value_rot, int interleaved, int H, int G, int dk, int dv, int v_row, int v_div,
-                               int block_size, int n_splits, float* workspace, int dtype, void* stream) {
+                               int heads_as_rows, int block_size, int n_splits, float* workspace, int dtype, void* stream) {
   if (chunk < 0 || v_row < dv || v_row % 8 || v_div < 1 || G % v_div)
     return fail(B200_EINVAL, "b200_mixed_prompt_attn: bad mask or value layout");
+  if (heads_as_rows && (G != 1 || talk || gate || value_rot))
+    return fail(B200_EINVAL, "b200_mixed_prompt_attn: heads as rows need one kv head and no mixing, gate or value rotation");
+  if (heads_as_rows && (!aligned16(q) || ((q_tok_stride | q_head_stride) & 7)))
+    return fail(B200_ESHAPE, "b200_mixed_prompt_attn: heads as rows need 16-byte aligned query rows");
+  const int H_real = H;
+  if (heads_as_rows) H = (H + 15) / 16;      // the kernel's heads are groups of 16 rows
   if (n_tiles < 0 || n_tok < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || block_size <= 0 || n_splits < 1 ||
       n_splits > 64)
     return fail(B200_EINVAL, "b200_mixed_prompt_attn: bad sizes");
@@ -1381,11 +1422,11 @@ int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_he
   if ((q_tok_stride | q_head_stride | out_tok_stride | out_head_stride) & 1)
     return fail(B200_ESHAPE, "b200_mixed_prompt_attn: odd strides");
   TcPlan plan;
-  if (!tc_plan(H, G, dk, dv, talk != nullptr, k_pool == v_pool, value_rot != nullptr, dtype, &plan))
+  if (!tc_plan(H, G, dk, dv, talk != nullptr, k_pool == v_pool, value_rot != nullptr, dtype, &plan, heads_as_rows != 0))
     return fail(B200_ESHAPE, "b200_mixed_prompt_attn: sizes off the tensor-core grid (dk %d, dv %d)", dk, dv);
   AttnArgs A{out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride, k_pool, v_pool,
              block_tables, table_stride, nullptr, tok_pos, talk, sink, scale, window, keep_first, value_rot != nullptr,
-             interleaved, 0.0, H, G, dk, dv, block_size, softcap, chunk, v_row, v_div};
+             interleaved, 0.0, H, G, dk, dv, block_size, softcap, chunk, v_row, v_div, heads_as_rows ? H_real : 0};
   const dim3 grid(n_tiles, (H + kTcWarps * plan.hw - 1) / (kTcWarps * plan.hw), n_splits);
   return hybrid_by_dtype(dtype, "b200_mixed_prompt_attn", [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
@@ -1399,15 +1440,25 @@ int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_he
         cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         kern<<<grid, kTcWarps * 32, plan.smem, s>>>(A, tiles, value_rot, workspace, n_tok, plan.stages);
       };
-      if (plan.dv8 == 8 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 8, 1>);
-      else if (plan.dv8 == 8) launch(mixed_prompt_attn_kernel<T, 8, 2>);
-      else if (plan.dv8 == 16 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 16, 1>);
-      else if (plan.dv8 == 16) launch(mixed_prompt_attn_kernel<T, 16, 2>);
-      else launch(mixed_prompt_attn_kernel<T, 32, 1>);
+      const bool ext = chunk > 0 || v_div > 1 || v_row != dv || heads_as_rows;
+      if (ext) {
+        if (plan.dv8 == 8 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 8, 1, true>);
+        else if (plan.dv8 == 8) launch(mixed_prompt_attn_kernel<T, 8, 2, true>);
+        else if (plan.dv8 == 16 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 16, 1, true>);
+        else if (plan.dv8 == 16) launch(mixed_prompt_attn_kernel<T, 16, 2, true>);
+        else launch(mixed_prompt_attn_kernel<T, 32, 1, true>);
+      } else {
+        if (plan.dv8 == 8 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 8, 1, false>);
+        else if (plan.dv8 == 8) launch(mixed_prompt_attn_kernel<T, 8, 2, false>);
+        else if (plan.dv8 == 16 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 16, 1, false>);
+        else if (plan.dv8 == 16) launch(mixed_prompt_attn_kernel<T, 16, 2, false>);
+        else launch(mixed_prompt_attn_kernel<T, 32, 1, false>);
+      }
       int rc = check_launch("b200_mixed_prompt_attn");
       if (rc != 0 || n_splits == 1) return rc;
       // every packed row belongs to exactly one tile, so the merge runs over all rows
-      const size_t smem_c = sizeof(float) * static_cast<size_t>(H) * dv;
+      A.H = H_real;
+      const size_t smem_c = sizeof(float) * static_cast<size_t>(H_real) * dv;
       auto comb = attn_split_combine_kernel<T>;
       if (smem_c > 48 * 1024) cudaFuncSetAttribute(comb, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem_c));
       comb<<<n_tok, 256, smem_c, s>>>(A, workspace, n_splits, n_tok, plan.dv8 * 8, value_rot);

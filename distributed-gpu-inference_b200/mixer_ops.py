@@ -458,13 +458,15 @@ def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Ten
                            talk: Optional[torch.Tensor] = None, sink: Optional[torch.Tensor] = None, window: int = 0,
                            keep_first: int = 0, value_rot: Optional[torch.Tensor] = None, interleaved: bool = False,
                            gate: Optional[torch.Tensor] = None, max_context: int = 0, softcap: float = 0.0,
-                           chunk: int = 0, value_width: Optional[int] = None, value_div: int = 1) -> None:
+                           chunk: int = 0, value_width: Optional[int] = None, value_div: int = 1,
+                           heads_as_rows: bool = False) -> None:
     """``mixed_paged_attention`` on the tensor cores for prompt portions and decoded tokens alike (16-bit dtypes, see
     ``mixed_prompt_attention_supported``).  ``tiles`` int32 ``[n_tiles, 3]``: up to ``PROMPT_TILE_TOKENS`` consecutive
     tokens of one sequence each, together covering every row of ``q``; ``value_rot``: the table ``rotary_kv_append``
     returned for this step's tokens; ``max_context``: the longest context of the step (a hint: steps of few tokens over
     long contexts divide the keys over several CTAs and merge); ``chunk``, ``value_width`` and ``value_div`` as in
-    ``mixed_paged_attention``."""
+    ``mixed_paged_attention``.  ``heads_as_rows`` (steps of single tokens over one kv head, no talk / gate / value_rot):
+    the 16 rows of a tensor-core tile are 16 query heads of one token instead of 16 tokens of one head."""
     _need_cuda(out, q, k_pool, v_pool, block_tables, tiles, tok_pos)
     nb, G, bs, dk = k_pool.shape
     dv, v_row = _value_layout(k_pool, v_pool, value_width, value_div)
@@ -483,11 +485,14 @@ def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Ten
         raise ValueError("value_rot must be contiguous fp32 [n, dv // 2, 2]")
     if gate is not None and (tuple(gate.shape) != (n, H) or gate.dtype != q.dtype):
         raise ValueError("gate must be [n, H] in the activations' dtype")
+    if heads_as_rows and (G != 1 or talk is not None or gate is not None or value_rot is not None):
+        raise ValueError("heads_as_rows needs one kv head and no talk, gate or value_rot")
     lib = _lib_()
     seen = min(max_context, window + keep_first + PROMPT_TILE_TOKENS) if window > 0 else max_context
     if chunk > 0:
         seen = min(seen, chunk + PROMPT_TILE_TOKENS)
-    splits = lib.b200_mixed_prompt_attn_splits(tiles.shape[0], (seen + 31) // 32, H, G, dk, dv, int(talk is not None),
+    splits = lib.b200_mixed_prompt_attn_splits(tiles.shape[0], (seen + 31) // 32, (H + 15) // 16 if heads_as_rows else H, G,
+                                               dk, dv, int(talk is not None),
                                                int(k_pool.data_ptr() == v_pool.data_ptr()), int(value_rot is not None),
                                                DTYPE_ID[q.dtype]) if max_context > 0 else 1
     ws = None
@@ -498,8 +503,8 @@ def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Ten
                                         v_pool.data_ptr(), block_tables.data_ptr(), block_tables.stride(0),
                                         tiles.data_ptr(), tiles.shape[0], tok_pos.data_ptr(), n, _ptr(talk), _ptr(sink),
                                         float(scale), float(softcap), int(window), int(keep_first), int(chunk),
-                                        _ptr(value_rot), int(interleaved), H, G, dk, dv, v_row, int(value_div), bs,
-                                        int(splits), _ptr(ws), DTYPE_ID[q.dtype], _stream())
+                                        _ptr(value_rot), int(interleaved), H, G, dk, dv, v_row, int(value_div),
+                                        int(heads_as_rows), bs, int(splits), _ptr(ws), DTYPE_ID[q.dtype], _stream())
     _lib.check_mixers(rc, "b200_mixed_prompt_attn")
 
 

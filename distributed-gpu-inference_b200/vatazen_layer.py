@@ -134,6 +134,8 @@ class LatentRotaryAttention(nn.Module):
     rotary + append, the batched key up-projection on the query side, attention, the batched value up-projection, the
     output GEMM."""
 
+    HEADS_AS_ROWS_FROM = 16    # heads from which a step of single tokens puts heads on the rows of the attention's tiles
+
     def __init__(self, spec: Dict[str, Any], t: Dict[str, torch.Tensor], eps: float, device, dtype):
         super().__init__()
         self.H, self.dn, self.dr = int(spec["heads"]), int(spec["dim"]), int(spec["rot_dim"])
@@ -169,9 +171,11 @@ class LatentRotaryAttention(nn.Module):
         o_lat = torch.empty((H, n, r), dtype=h.dtype, device=h.device)
         if self.tensor_cores:
             tiles, _ = st.prompt_tiles(1, mixer_ops.PROMPT_TILE_TOKENS)
+            # steps of single tokens: all heads read the same rows, so 16 heads share a tensor-core tile
             mixer_ops.mixed_prompt_attention(o_lat.transpose(0, 1), q_lat, cache.k_pool, cache.k_pool, st.block_tables,
                                              tiles, st.tok_pos, self.scale, sink=self.sink, window=self.window,
-                                             max_context=st.max_context(), value_width=r)
+                                             max_context=st.max_context(), value_width=r,
+                                             heads_as_rows=H >= self.HEADS_AS_ROWS_FROM and st.max_count() == 1)
         else:
             mixer_ops.mixed_paged_attention(o_lat.transpose(0, 1), q_lat, cache.k_pool, cache.k_pool, st.block_tables,
                                             st.tok_row, st.tok_pos, self.scale, sink=self.sink, window=self.window,

@@ -193,14 +193,17 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
                            int H, int G, int dk, int dv, int block_size, int n_splits, float* workspace, int dtype,
                            void* stream);
 
-/* b200_mixed_prompt_attn with chunk, v_row and v_div as in b200_mixed_paged_attn_ext (v_row a multiple of 8). */
+/* b200_mixed_prompt_attn with chunk, v_row and v_div as in b200_mixed_paged_attn_ext (v_row a multiple of 8).
+ * heads_as_rows != 0 (steps of single tokens over ONE kv head, G == 1, no talk / gate / value_rot): every tile is one
+ * token (count 1) and the 16 rows of a tensor-core tile are 16 consecutive query heads instead of 16 tokens, so a warp
+ * serves 16 heads against the staged keys.  For b200_mixed_prompt_attn_splits such a step counts (H + 15) / 16 heads. */
 int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q,
                                int64_t q_tok_stride, int64_t q_head_stride, const void* gate, int64_t gate_stride,
                                const void* k_pool, const void* v_pool, const int32_t* block_tables, int table_stride,
                                const int32_t* tiles, int n_tiles, const int32_t* tok_pos, int n_tok, const float* talk,
                                const float* sink, float scale, float softcap, int window, int keep_first, int chunk,
                                const float* value_rot, int interleaved, int H, int G, int dk, int dv, int v_row, int v_div,
-                               int block_size, int n_splits, float* workspace, int dtype, void* stream);
+                               int heads_as_rows, int block_size, int n_splits, float* workspace, int dtype, void* stream);
 
 /* out[t, c] = silu(sum_i w[c][i] * x[t - (taps - 1 - i), c]) per sequence (SeqSpan rows); inputs before the portion
  * come from tail [slots, taps - 1, C] (fp32, oldest first), which then receives the portion's last taps - 1 inputs. */

@@ -66,6 +66,11 @@ CFG_B = {   # sizes the tensor-core attention and the grouped expert GEMM take i
         layer("attention", differential(4, 4, 32, 8, 5, 0.1), moe(8, 1, 16)),
     ],
 }
+CFG_D = {   # many heads over one latent row: steps of single tokens put the heads on the rows of the attention's tiles
+    "architecture": "Vatazen", "width": 64, "vocab": 37, "norm": {"eps": 1e-6}, "token_side": {"dim": 8},
+    "layers": [layer("latent_attention", latent(20, 8, 8, 8, 24, 11, base=100.0), moe(4, 2, 16)),
+               layer("latent_attention", latent(16, 16, 16, 16, 48, 300), None)],
+}
 CFG_C = {   # the smallest of everything, without the token table and the embedding scale
     "architecture": "Vatazen", "width": 16, "vocab": 11, "norm": {"eps": 1e-6},
     "layers": [layer("latent_attention", latent(1, 2, 2, 2, 4, 1), moe(1, 1, 8)),
@@ -291,7 +296,8 @@ def test_block_edges_and_two_maps_over_one_value_head_fp32():
 
 
 @pytest.mark.parametrize("dt", [torch.bfloat16, torch.float16], ids=["bf16", "fp16"])
-@pytest.mark.parametrize("H,D,rank,win", [(10, 64, 48, 19), (2, 80, 72, 40), (16, 192, 128, 33), (3, 48, 8, 1)])
+@pytest.mark.parametrize("H,D,rank,win", [(10, 64, 48, 19), (2, 80, 72, 40), (16, 192, 128, 33), (3, 48, 8, 1), (37, 96, 64, 70),
+                                          (32, 320, 256, 100)])
 def test_tensor_core_latent_attention_matches_the_statement(dt, H, D, rank, win):
     from dgi_b200 import mixer_ops as M
 
@@ -320,6 +326,14 @@ def test_tensor_core_latent_attention_matches_the_statement(dt, H, D, rank, win)
                              torch.tensor([(0, 1, 0), (1, 1, 1), (2, 1, 2)], dtype=torch.int32, device=DEV),
                              last.to(torch.int32).to(DEV), 0.2, sink=sink.to(DEV), window=win, max_context=n, value_width=rank)
     close(out.cpu(), ref[last], tol)
+    # the same three tokens with 16 heads on the rows of a tile, head-major outputs, with and without key splits
+    for ctx in (n, 0):
+        out = torch.full((H, 3, rank), float("nan"), dtype=dt, device=DEV).transpose(0, 1)
+        M.mixed_prompt_attention(out, q[last].to(DEV), pool, pool, table.expand(3, -1).contiguous(),
+                                 torch.tensor([(0, 1, 0), (1, 1, 1), (2, 1, 2)], dtype=torch.int32, device=DEV),
+                                 last.to(torch.int32).to(DEV), 0.2, sink=sink.to(DEV), window=win, max_context=ctx,
+                                 value_width=rank, heads_as_rows=True)
+        close(out.cpu(), ref[last], tol)
     # and the row kernel says the same
     out2 = torch.empty((n, H, rank), dtype=dt, device=DEV)
     M.mixed_paged_attention(out2, q.to(DEV), pool, pool, table, torch.zeros(n, dtype=torch.int32, device=DEV), pos, 0.2,
@@ -570,6 +584,27 @@ def test_long_prompt_whole_in_portions_and_decoded_bf16_against_fp32():
     got += [e16.step([("b", [t], [0] if i in (0, 9) else [])]) for i, t in enumerate(toks[590:])]
     e16.release()
     rounding_close(torch.cat([g for g in got if g is not None]).cpu(), ref)
+
+
+def test_single_token_steps_with_heads_on_the_rows_bf16_against_fp32():
+    cfg = CFG_D
+    e32, _ = build(cfg, max_tokens=512, max_seqs=3)
+    e16, _ = build(cfg, dtype=torch.bfloat16, max_tokens=512, max_seqs=3)
+    prompts = {r: tokens(n, cfg["vocab"], 60 + i) for i, (r, n) in enumerate((("a", 150), ("b", 40), ("c", 75)))}
+    ref = {r: whole(e32, r, t) for r, t in prompts.items()}
+    got = {r: [] for r in prompts}
+    out = e16.step([(r, t[:len(t) - 30], list(range(len(t) - 30))) for r, t in prompts.items()])
+    o = 0
+    for r, t in prompts.items():
+        got[r].append(out[o:o + len(t) - 30])
+        o += len(t) - 30
+    for i in range(30):                                       # 30 steps of three single tokens
+        out = e16.step([(r, [t[len(t) - 30 + i]], [0]) for r, t in prompts.items()])
+        for j, r in enumerate(prompts):
+            got[r].append(out[j:j + 1])
+    e16.release()
+    for r in prompts:
+        rounding_close(torch.cat(got[r]).cpu(), ref[r])
 
 
 def test_greedy_generation_through_the_scheduler():
