@@ -188,11 +188,12 @@ MIXER_SIGNATURES = {
     "b200_mixed_paged_attn_ext": (
         c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                 c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int, c_int, c_int,
-                c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                c_float, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_mixed_prompt_attn_ext": (
         c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_void_p,
                 c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_float, c_float, c_int, c_int, c_int,
-                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p]),
+                c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_int,
+                c_void_p]),
     "b200_qknorm_rotary_append_ext": (
         c_int, [c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_int64, c_void_p, c_void_p, c_float, c_void_p, c_int, c_int,
                 c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int64, c_int,
@@ -204,7 +205,7 @@ MIXER_SIGNATURES = {
         c_int, [c_void_p, c_int64, c_int64, c_void_p, c_int64, c_int64, c_void_p, c_int64, c_void_p, c_float, c_void_p,
                 c_float, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "b200_head_diff_norm": (
-        c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_float, c_float, c_float, c_int64, c_int, c_int, c_int,
+        c_int, [c_void_p, c_int64, c_void_p, c_int64, c_int64, c_int, c_float, c_float, c_float, c_int64, c_int, c_int, c_int,
                 c_int, c_void_p]),
     "b200_gated_postnorm_residual": (
         c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_float, c_int, c_int,

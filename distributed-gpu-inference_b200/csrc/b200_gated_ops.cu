@@ -150,26 +150,26 @@ latent_rotary_append_kernel(const T* __restrict__ q_rot, int64_t q_tok_stride, i
 
 // ---- head difference norm ------------------------------------------------------------------------------------------
 // One warp per (token, head).  The two maps of head h sit at heads (h / rep) * 2 rep + (h % rep) and that + rep of `a`.
-template <typename T>
+template <typename T, typename A>
 __global__ void __launch_bounds__(256)
-head_diff_norm_kernel(T* __restrict__ out, int64_t out_stride, const T* __restrict__ a, int64_t a_tok_stride,
+head_diff_norm_kernel(T* __restrict__ out, int64_t out_stride, const A* __restrict__ a, int64_t a_tok_stride,
                       int64_t a_head_stride, float lam, float out_scale, float eps, int64_t rows, int H, int rep, int dv) {
   const int64_t r = static_cast<int64_t>(blockIdx.x) * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (r >= rows) return;
   const int lane = threadIdx.x & 31;
   const int64_t n = r / H;
   const int h = static_cast<int>(r - n * H);
-  const T* a1 = a + n * a_tok_stride + ((h / rep) * 2 * rep + (h % rep)) * a_head_stride;
-  const T* a2 = a1 + rep * a_head_stride;
+  const A* a1 = a + n * a_tok_stride + ((h / rep) * 2 * rep + (h % rep)) * a_head_stride;
+  const A* a2 = a1 + rep * a_head_stride;
   float ss = 0.f;
   for (int i = lane; i < dv; i += 32) {
-    const float o = fmaf(-lam, Cvt<T>::to_f32(a2[i]), Cvt<T>::to_f32(a1[i]));
+    const float o = fmaf(-lam, Cvt<A>::to_f32(a2[i]), Cvt<A>::to_f32(a1[i]));
     ss = fmaf(o, o, ss);
   }
   const float f = rsqrtf(warp_sum(ss) / static_cast<float>(dv) + eps) * out_scale;
   T* dst = out + n * out_stride + static_cast<int64_t>(h) * dv;
   for (int i = lane; i < dv; i += 32)
-    dst[i] = Cvt<T>::from_f32(fmaf(-lam, Cvt<T>::to_f32(a2[i]), Cvt<T>::to_f32(a1[i])) * f);
+    dst[i] = Cvt<T>::from_f32(fmaf(-lam, Cvt<A>::to_f32(a2[i]), Cvt<A>::to_f32(a1[i])) * f);
 }
 
 // ---- gated post-norm residual --------------------------------------------------------------------------------------
@@ -297,17 +297,23 @@ int b200_latent_rotary_append(const void* q_rot, int64_t q_tok_stride, int64_t q
   });
 }
 
-int b200_head_diff_norm(void* out, int64_t out_stride, const void* a, int64_t a_tok_stride, int64_t a_head_stride, float lam,
-                        float out_scale, float eps, int64_t n_tok, int H, int rep, int dv, int dtype, void* stream) {
+int b200_head_diff_norm(void* out, int64_t out_stride, const void* a, int64_t a_tok_stride, int64_t a_head_stride,
+                        int a_is_f32, float lam, float out_scale, float eps, int64_t n_tok, int H, int rep, int dv, int dtype,
+                        void* stream) {
   if (n_tok < 0 || H <= 0 || rep <= 0 || H % rep || dv <= 0) return fail(B200_EINVAL, "b200_head_diff_norm: bad sizes");
   if (n_tok == 0) return 0;
   if (!out || !a) return fail(B200_EINVAL, "b200_head_diff_norm: null pointer");
   const int64_t rows = n_tok * H;
   return gated_by_dtype(dtype, "b200_head_diff_norm", [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
-    head_diff_norm_kernel<T><<<static_cast<unsigned>((rows + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        static_cast<T*>(out), out_stride, static_cast<const T*>(a), a_tok_stride, a_head_stride, lam, out_scale, eps, rows,
-        H, rep, dv);
+    const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
+    auto s = static_cast<cudaStream_t>(stream);
+    if (a_is_f32)
+      head_diff_norm_kernel<T, float><<<grid, 256, 0, s>>>(static_cast<T*>(out), out_stride, static_cast<const float*>(a),
+                                                           a_tok_stride, a_head_stride, lam, out_scale, eps, rows, H, rep, dv);
+    else
+      head_diff_norm_kernel<T, T><<<grid, 256, 0, s>>>(static_cast<T*>(out), out_stride, static_cast<const T*>(a),
+                                                       a_tok_stride, a_head_stride, lam, out_scale, eps, rows, H, rep, dv);
     return check_launch("b200_head_diff_norm");
   });
 }

@@ -264,6 +264,7 @@ struct AttnArgs {
   int v_div = 1;   // value head = key head / v_div (several key heads read one value head)
   int row_heads = 0;   // tensor-core kernel, > 0: a tile is ONE token and its 16 rows are consecutive heads of `row_heads`
                        // that share one kv head; H then counts groups of 16 heads
+  int out_f32 = 0;     // != 0: `out` is fp32 (same strides, in elements) whatever T is; plain outputs only (no turn back)
 };
 
 // first key a position sees (the kept first tokens of a window aside)
@@ -462,7 +463,8 @@ mixed_paged_attn_kernel(const AttnArgs A) {
       if (h0 + hl >= H) continue;
       float y = res[e];
       if (gate) y *= sigmoid_(Cvt<T>::to_f32(gate[static_cast<int64_t>(n) * A.gate_stride + h0 + hl]));
-      out[(h0 + hl) * A.out_head_stride + c] = Cvt<T>::from_f32(y);
+      if (A.out_f32) static_cast<float*>(A.out)[static_cast<int64_t>(n) * A.out_tok_stride + (h0 + hl) * A.out_head_stride + c] = y;
+      else out[(h0 + hl) * A.out_head_stride + c] = Cvt<T>::from_f32(y);
     }
   }
 }
@@ -832,7 +834,11 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
 #pragma unroll
         for (int nt = 0; nt < DV8; ++nt) {
           const int c = nt * 8 + qc;
-          if (c < dv) *reinterpret_cast<uint32_t*>(orow + c) = Mma16x8<T>::pack(O[hw][nt][2 * half], O[hw][nt][2 * half + 1]);
+          if (c >= dv) continue;
+          if (EXT && A.out_f32)
+            *reinterpret_cast<float2*>(static_cast<float*>(A.out) + (orow - outp) + c) = make_float2(O[hw][nt][2 * half], O[hw][nt][2 * half + 1]);
+          else
+            *reinterpret_cast<uint32_t*>(orow + c) = Mma16x8<T>::pack(O[hw][nt][2 * half], O[hw][nt][2 * half + 1]);
         }
       }
     } else {
@@ -918,7 +924,8 @@ attn_split_combine_kernel(const AttnArgs A, const float* __restrict__ ws, int n_
       const int h = e / dv, c = e - h * dv;
       float y = res[e];
       if (gate) y *= sigmoid_(Cvt<T>::to_f32(gate[static_cast<int64_t>(n) * A.gate_stride + h]));
-      out[h * A.out_head_stride + c] = Cvt<T>::from_f32(y);
+      if (A.out_f32) static_cast<float*>(A.out)[static_cast<int64_t>(n) * A.out_tok_stride + h * A.out_head_stride + c] = y;
+      else out[h * A.out_head_stride + c] = Cvt<T>::from_f32(y);
     }
   }
 }
@@ -1320,7 +1327,7 @@ int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_st
                           int G, int dk, int dv, int block_size, int dtype, void* stream) {
   return b200_mixed_paged_attn_ext(out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride,
                                    k_pool, v_pool, block_tables, table_stride, tok_row, tok_pos, n_tok, talk, sink, scale,
-                                   softcap, window, keep_first, 0, unrotate, interleaved, rot_base, H, G, dk, dv, dv, 1,
+                                   softcap, window, keep_first, 0, unrotate, interleaved, rot_base, H, G, dk, dv, dv, 1, 0,
                                    block_size, dtype, stream);
 }
 
@@ -1330,7 +1337,8 @@ int b200_mixed_paged_attn_ext(void* out, int64_t out_tok_stride, int64_t out_hea
                               const int32_t* tok_row, const int32_t* tok_pos, int n_tok, const float* talk,
                               const float* sink, float scale, float softcap, int window, int keep_first, int chunk,
                               int unrotate, int interleaved, float rot_base, int H, int G, int dk, int dv, int v_row,
-                              int v_div, int block_size, int dtype, void* stream) {
+                              int v_div, int out_f32, int block_size, int dtype, void* stream) {
+  if (out_f32 && unrotate) return fail(B200_EINVAL, "b200_mixed_paged_attn: fp32 outputs are not turned back");
   if (n_tok < 0 || H <= 0 || G <= 0 || H % G || dk <= 0 || dv <= 0 || block_size <= 0 || chunk < 0 || v_row < dv ||
       v_div < 1 || G % v_div)
     return fail(B200_EINVAL, "b200_mixed_paged_attn: bad sizes");
@@ -1340,7 +1348,7 @@ int b200_mixed_paged_attn_ext(void* out, int64_t out_tok_stride, int64_t out_hea
     return fail(B200_EINVAL, "b200_mixed_paged_attn: null pointer");
   AttnArgs A{out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride, k_pool, v_pool,
              block_tables, table_stride, tok_row, tok_pos, talk, sink, scale, window, keep_first, unrotate, interleaved,
-             static_cast<double>(rot_base), H, G, dk, dv, block_size, softcap, chunk, v_row, v_div};
+             static_cast<double>(rot_base), H, G, dk, dv, block_size, softcap, chunk, v_row, v_div, 0, out_f32};
   const int dvc = dv <= 64 ? 2 : (dv <= 128 ? 4 : (dv <= 256 ? 8 : 16));
   const int hp = dvc <= 4 ? 8 : (dvc == 8 ? 4 : 2);
   const int nhs = talk ? H : std::min(hp, H);
@@ -1394,7 +1402,7 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
                            void* stream) {
   return b200_mixed_prompt_attn_ext(out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride,
                                     k_pool, v_pool, block_tables, table_stride, tiles, n_tiles, tok_pos, n_tok, talk, sink,
-                                    scale, softcap, window, keep_first, 0, value_rot, interleaved, H, G, dk, dv, dv, 1, 0,
+                                    scale, softcap, window, keep_first, 0, value_rot, interleaved, H, G, dk, dv, dv, 1, 0, 0,
                                     block_size, n_splits, workspace, dtype, stream);
 }
 
@@ -1404,7 +1412,9 @@ int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_he
                                const int32_t* tiles, int n_tiles, const int32_t* tok_pos, int n_tok, const float* talk,
                                const float* sink, float scale, float softcap, int window, int keep_first, int chunk,
                                const float* value_rot, int interleaved, int H, int G, int dk, int dv, int v_row, int v_div,
-                               int heads_as_rows, int block_size, int n_splits, float* workspace, int dtype, void* stream) {
+                               int heads_as_rows, int out_f32, int block_size, int n_splits, float* workspace, int dtype,
+                               void* stream) {
+  if (out_f32 && value_rot) return fail(B200_EINVAL, "b200_mixed_prompt_attn: fp32 outputs are not turned back");
   if (chunk < 0 || v_row < dv || v_row % 8 || v_div < 1 || G % v_div)
     return fail(B200_EINVAL, "b200_mixed_prompt_attn: bad mask or value layout");
   if (heads_as_rows && (G != 1 || talk || gate || value_rot))
@@ -1426,7 +1436,8 @@ int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_he
     return fail(B200_ESHAPE, "b200_mixed_prompt_attn: sizes off the tensor-core grid (dk %d, dv %d)", dk, dv);
   AttnArgs A{out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride, k_pool, v_pool,
              block_tables, table_stride, nullptr, tok_pos, talk, sink, scale, window, keep_first, value_rot != nullptr,
-             interleaved, 0.0, H, G, dk, dv, block_size, softcap, chunk, v_row, v_div, heads_as_rows ? H_real : 0};
+             interleaved, 0.0, H, G, dk, dv, block_size, softcap, chunk, v_row, v_div, heads_as_rows ? H_real : 0,
+             out_f32};
   const dim3 grid(n_tiles, (H + kTcWarps * plan.hw - 1) / (kTcWarps * plan.hw), n_splits);
   return hybrid_by_dtype(dtype, "b200_mixed_prompt_attn", [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
@@ -1440,7 +1451,7 @@ int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_he
         cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         kern<<<grid, kTcWarps * 32, plan.smem, s>>>(A, tiles, value_rot, workspace, n_tok, plan.stages);
       };
-      const bool ext = chunk > 0 || v_div > 1 || v_row != dv || heads_as_rows;
+      const bool ext = chunk > 0 || v_div > 1 || v_row != dv || heads_as_rows || out_f32;
       if (ext) {
         if (plan.dv8 == 8 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 8, 1, true>);
         else if (plan.dv8 == 8) launch(mixed_prompt_attn_kernel<T, 8, 2, true>);

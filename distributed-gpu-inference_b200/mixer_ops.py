@@ -415,15 +415,17 @@ def mixed_paged_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tens
     bounds the scores by ``softcap * tanh(score / softcap)`` before the mask, ``chunk`` > 0 lets a position see only
     the keys of its own block of ``chunk`` positions, ``value_width`` says that the values are the first that many
     columns of the (wider) rows of ``v_pool``, ``value_div`` that ``v_pool`` holds one value head per that many key
-    heads (several score maps over the same values)."""
+    heads (several score maps over the same values).  ``out`` may be fp32 whatever the storage dtype (results that are
+    combined before they are rounded; not with ``unrotate_base``)."""
     _need_cuda(out, q, k_pool, v_pool, block_tables, tok_row, tok_pos)
     nb, G, bs, dk = k_pool.shape
     dv, v_row = _value_layout(k_pool, v_pool, value_width, value_div)
     n, H = q.shape[0], q.shape[1]
     if q.dim() != 3 or q.shape[2] != dk or tuple(out.shape) != (n, H, dv) or q.stride(2) != 1 or out.stride(2) != 1:
         raise ValueError("q must be [n, H, dk] and out [n, H, dv] with contiguous last dimensions")
-    if out.dtype != q.dtype or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
-        raise TypeError("q, out and the pools share one dtype")
+    if out.dtype not in (q.dtype, torch.float32) or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
+        raise TypeError("q and the pools share one dtype; out has it too, or is fp32")
+    out_f32 = int(out.dtype == torch.float32 and q.dtype != torch.float32)
     for t in (block_tables, tok_row, tok_pos):
         if t.dtype != torch.int32:
             raise TypeError("block tables, token rows and positions are int32")
@@ -438,7 +440,7 @@ def mixed_paged_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Tens
                                            block_tables.stride(0), tok_row.data_ptr(), tok_pos.data_ptr(), n, _ptr(talk),
                                            _ptr(sink), float(scale), float(softcap), int(window), int(keep_first),
                                            int(chunk), int(unrotate_base is not None), int(interleaved),
-                                           float(unrotate_base or 0.0), H, G, dk, dv, v_row, int(value_div), bs,
+                                           float(unrotate_base or 0.0), H, G, dk, dv, v_row, int(value_div), out_f32, bs,
                                            DTYPE_ID[q.dtype], _stream())
     _lib.check_mixers(rc, "b200_mixed_paged_attn")
 
@@ -473,8 +475,9 @@ def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Ten
     n, H = q.shape[0], q.shape[1]
     if q.dim() != 3 or q.shape[2] != dk or tuple(out.shape) != (n, H, dv) or q.stride(2) != 1 or out.stride(2) != 1:
         raise ValueError("q must be [n, H, dk] and out [n, H, dv] with contiguous last dimensions")
-    if out.dtype != q.dtype or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
-        raise TypeError("q, out and the pools share one dtype")
+    if out.dtype not in (q.dtype, torch.float32) or k_pool.dtype != q.dtype or v_pool.dtype != q.dtype:
+        raise TypeError("q and the pools share one dtype; out has it too, or is fp32")
+    out_f32 = int(out.dtype == torch.float32 and q.dtype != torch.float32)
     if tiles.dtype != torch.int32 or tiles.dim() != 2 or tiles.shape[1] != 3 or not tiles.is_contiguous():
         raise ValueError("tiles must be contiguous int32 [n_tiles, 3]")
     for t, shape in ((talk, (H, H)), (sink, (H,))):
@@ -504,7 +507,7 @@ def mixed_prompt_attention(out: torch.Tensor, q: torch.Tensor, k_pool: torch.Ten
                                         tiles.data_ptr(), tiles.shape[0], tok_pos.data_ptr(), n, _ptr(talk), _ptr(sink),
                                         float(scale), float(softcap), int(window), int(keep_first), int(chunk),
                                         _ptr(value_rot), int(interleaved), H, G, dk, dv, v_row, int(value_div),
-                                        int(heads_as_rows), bs, int(splits), _ptr(ws), DTYPE_ID[q.dtype], _stream())
+                                        int(heads_as_rows), out_f32, bs, int(splits), _ptr(ws), DTYPE_ID[q.dtype], _stream())
     _lib.check_mixers(rc, "b200_mixed_prompt_attn")
 
 
@@ -842,20 +845,24 @@ def latent_rotary_append(q_rot: torch.Tensor, q_out: torch.Tensor, dkv: torch.Te
 
 
 @_timed
-def head_diff_norm(a: torch.Tensor, lam: float, out_scale: float, eps: float, rep: int, out: Optional[torch.Tensor] = None
-                   ) -> torch.Tensor:
-    """``a [n, 2H, dv]`` (a view with a contiguous last dimension) holds two score maps' outputs per head, map 1 of head
-    ``h`` at ``(h // rep) * 2 rep + h % rep`` and map 2 ``rep`` heads further: returns ``[n, H * dv]`` =
-    ``unit_rms(a1 - lam a2) * out_scale`` per head."""
+def head_diff_norm(a: torch.Tensor, lam: float, out_scale: float, eps: float, rep: int, dtype: Optional[torch.dtype] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``a [n, 2H, dv]`` (a view with a contiguous last dimension; fp32 or the storage dtype) holds two score maps'
+    outputs per head, map 1 of head ``h`` at ``(h // rep) * 2 rep + h % rep`` and map 2 ``rep`` heads further: returns
+    ``[n, H * dv]`` = ``unit_rms(a1 - lam a2) * out_scale`` per head in ``dtype`` (default: ``a``'s)."""
     _need_cuda(a)
+    dtype = dtype or (out.dtype if out is not None else a.dtype)
+    if a.dtype not in (dtype, torch.float32):
+        raise TypeError("a is fp32 or of the output's dtype")
     n, H2, dv = a.shape
     if a.stride(2) != 1 or H2 % (2 * rep):
         raise ValueError("a is [n, 2H, dv] with a contiguous last dimension, H a multiple of rep")
     H = H2 // 2
     if out is None:
-        out = torch.empty((n, H * dv), dtype=a.dtype, device=a.device)
-    rc = _lib_().b200_head_diff_norm(out.data_ptr(), _rows2(out), a.data_ptr(), a.stride(0), a.stride(1), float(lam),
-                                     float(out_scale), float(eps), n, H, int(rep), dv, DTYPE_ID[a.dtype], _stream())
+        out = torch.empty((n, H * dv), dtype=dtype, device=a.device)
+    rc = _lib_().b200_head_diff_norm(out.data_ptr(), _rows2(out), a.data_ptr(), a.stride(0), a.stride(1),
+                                     int(a.dtype == torch.float32 and dtype != torch.float32), float(lam), float(out_scale),
+                                     float(eps), n, H, int(rep), dv, DTYPE_ID[dtype], _stream())
     _lib.check_mixers(rc, "b200_head_diff_norm")
     return out
 

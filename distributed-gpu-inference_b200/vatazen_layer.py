@@ -230,7 +230,7 @@ class DifferentialAttention(nn.Module):
         k_pool = cache.k_pool.view(nb, 2 * G, bs, dk)        # the pool's rows as (kv head, map) key heads
         mixer_ops.qknorm_rotary_append(q, k, v, self.q_norm, self.k_norm, self.eps, None, k_pool, cache.v_pool,
                                        st.slot_mapping, st.tok_pos, 2 * H)
-        maps = torch.empty((n, 2 * H, dv), dtype=h.dtype, device=h.device)
+        maps = torch.empty((n, 2 * H, dv), dtype=torch.float32, device=h.device)    # rounded only after their difference
         if self.tensor_cores:
             tiles, _ = st.prompt_tiles(1, mixer_ops.PROMPT_TILE_TOKENS)
             mixer_ops.mixed_prompt_attention(maps, q.unflatten(1, (2 * H, dk)), k_pool, cache.v_pool, st.block_tables, tiles,
@@ -239,7 +239,7 @@ class DifferentialAttention(nn.Module):
         else:
             mixer_ops.mixed_paged_attention(maps, q.unflatten(1, (2 * H, dk)), k_pool, cache.v_pool, st.block_tables,
                                             st.tok_row, st.tok_pos, self.scale, chunk=self.chunk, value_div=2)
-        o = mixer_ops.head_diff_norm(maps, self.lam, 1.0 - self.diff, self.eps, self.rep)
+        o = mixer_ops.head_diff_norm(maps, self.lam, 1.0 - self.diff, self.eps, self.rep, dtype=h.dtype)
         return F.linear(o, self.w_o, self.b_o)
 
 

@@ -162,14 +162,15 @@ int b200_mixed_paged_attn(void* out, int64_t out_tok_stride, int64_t out_head_st
  * counted from position 0 of the sequence).  v_row: elements between value rows of v_pool, so that the values may be the
  * first dv columns of wider rows (v_pool == k_pool with one kv head: a latent row serves as key over its whole width dk
  * and as value over its first dv columns).  v_div: value head = key head / v_div; v_pool holds G / v_div heads per block
- * (several score maps over the same values). */
+ * (several score maps over the same values).  out_f32 != 0: `out` is fp32 whatever T is (strides in elements; not with
+ * unrotate), for results that are combined before they are rounded. */
 int b200_mixed_paged_attn_ext(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q,
                               int64_t q_tok_stride, int64_t q_head_stride, const void* gate, int64_t gate_stride,
                               const void* k_pool, const void* v_pool, const int32_t* block_tables, int table_stride,
                               const int32_t* tok_row, const int32_t* tok_pos, int n_tok, const float* talk,
                               const float* sink, float scale, float softcap, int window, int keep_first, int chunk,
                               int unrotate, int interleaved, float rot_base, int H, int G, int dk, int dv, int v_row,
-                              int v_div, int block_size, int dtype, void* stream);
+                              int v_div, int out_f32, int block_size, int dtype, void* stream);
 
 /* The same attention on the tensor cores (16-bit T; dk a multiple of 16, dv a multiple of 8 up to 256, and a shared-
  * memory budget that b200_mixed_prompt_attn_supported checks; same_pool: keys and values are one pool).  tiles: int32
@@ -196,14 +197,16 @@ int b200_mixed_prompt_attn(void* out, int64_t out_tok_stride, int64_t out_head_s
 /* b200_mixed_prompt_attn with chunk, v_row and v_div as in b200_mixed_paged_attn_ext (v_row a multiple of 8).
  * heads_as_rows != 0 (steps of single tokens over ONE kv head, G == 1, no talk / gate / value_rot): every tile is one
  * token (count 1) and the 16 rows of a tensor-core tile are 16 consecutive query heads instead of 16 tokens, so a warp
- * serves 16 heads against the staged keys.  For b200_mixed_prompt_attn_splits such a step counts (H + 15) / 16 heads. */
+ * serves 16 heads against the staged keys.  For b200_mixed_prompt_attn_splits such a step counts (H + 15) / 16 heads.
+ * out_f32 as in b200_mixed_paged_attn_ext (not with value_rot). */
 int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_head_stride, const void* q,
                                int64_t q_tok_stride, int64_t q_head_stride, const void* gate, int64_t gate_stride,
                                const void* k_pool, const void* v_pool, const int32_t* block_tables, int table_stride,
                                const int32_t* tiles, int n_tiles, const int32_t* tok_pos, int n_tok, const float* talk,
                                const float* sink, float scale, float softcap, int window, int keep_first, int chunk,
                                const float* value_rot, int interleaved, int H, int G, int dk, int dv, int v_row, int v_div,
-                               int heads_as_rows, int block_size, int n_splits, float* workspace, int dtype, void* stream);
+                               int heads_as_rows, int out_f32, int block_size, int n_splits, float* workspace, int dtype,
+                               void* stream);
 
 /* out[t, c] = silu(sum_i w[c][i] * x[t - (taps - 1 - i), c]) per sequence (SeqSpan rows); inputs before the portion
  * come from tail [slots, taps - 1, C] (fp32, oldest first), which then receives the portion's last taps - 1 inputs. */
@@ -320,10 +323,11 @@ int b200_latent_rotary_append(const void* q_rot, int64_t q_tok_stride, int64_t q
                               int rank, int dtype, void* stream);
 
 /* Two score maps per head over the same values: with a1, a2 = a[n, (h / rep) * 2 rep + (h % rep) (+ rep), :],
- * out[n, h * dv + i] = o_i * rsqrt(mean_i o^2 + eps) * out_scale, o = a1 - lam * a2.  a: T, element (n, head, i) at
+ * out[n, h * dv + i] = o_i * rsqrt(mean_i o^2 + eps) * out_scale, o = a1 - lam * a2.  a: T or fp32 (a_is_f32), element (n, head, i) at
  * n * a_tok_stride + head * a_head_stride + i; out T rows with stride out_stride. */
-int b200_head_diff_norm(void* out, int64_t out_stride, const void* a, int64_t a_tok_stride, int64_t a_head_stride, float lam,
-                        float out_scale, float eps, int64_t n_tok, int H, int rep, int dv, int dtype, void* stream);
+int b200_head_diff_norm(void* out, int64_t out_stride, const void* a, int64_t a_tok_stride, int64_t a_head_stride,
+                        int a_is_f32, float lam, float out_scale, float eps, int64_t n_tok, int H, int rep, int dv, int dtype,
+                        void* stream);
 
 /* y = a * sigmoid(gate) (gate T rows, may be NULL);  x += (weight_offset + w_norm) * y * rsqrt(mean(y^2) + eps)  in place
  * on the fp32 residual; x_out (T, may be NULL) receives the new x.  a is fp32 (a_is_f32) or T. */

@@ -360,19 +360,21 @@ def test_tensor_core_differential_maps_match_the_statement(dt, H, G, dk, dv, chu
     tol = 2e-2 if dt == torch.bfloat16 else 4e-3
     for cuts in ([16] * 9 + [6], [5, 16, 3, 16, 16, 1, 13, 16, 16, 16, 16, 16]):
         tiles, at = tiles_of(cuts)
-        out = torch.full((n, 2 * H, dv), float("nan"), dtype=dt, device=DEV)
-        M.mixed_prompt_attention(out, q.to(DEV), kp, vp, table, tiles, pos, 0.25, chunk=chunk, value_div=2)
-        close(out[:at].cpu(), ref[:at], tol)
+        for odt in (dt, torch.float32):                      # outputs in the storage type, and unrounded
+            out = torch.full((n, 2 * H, dv), float("nan"), dtype=odt, device=DEV)
+            M.mixed_prompt_attention(out, q.to(DEV), kp, vp, table, tiles, pos, 0.25, chunk=chunk, value_div=2)
+            close(out[:at].cpu(), ref[:at], tol)
     last = torch.tensor([n - 1, first, max(first - 1, 0)])
-    out = torch.empty((3, 2 * H, dv), dtype=dt, device=DEV)
+    out = torch.empty((3, 2 * H, dv), dtype=torch.float32, device=DEV)
     M.mixed_prompt_attention(out, q[last].to(DEV), kp, vp, table.expand(3, -1).contiguous(),
                              torch.tensor([(0, 1, 0), (1, 1, 1), (2, 1, 2)], dtype=torch.int32, device=DEV),
                              last.to(torch.int32).to(DEV), 0.25, chunk=chunk, max_context=n, value_div=2)
     close(out.cpu(), ref[last], tol)
-    out2 = torch.empty((n, 2 * H, dv), dtype=dt, device=DEV)
-    M.mixed_paged_attention(out2, q.to(DEV), kp, vp, table, torch.zeros(n, dtype=torch.int32, device=DEV), pos, 0.25,
-                            chunk=chunk, value_div=2)
-    close(out2.cpu(), ref, tol)
+    for odt in (dt, torch.float32):
+        out2 = torch.empty((n, 2 * H, dv), dtype=odt, device=DEV)
+        M.mixed_paged_attention(out2, q.to(DEV), kp, vp, table, torch.zeros(n, dtype=torch.int32, device=DEV), pos, 0.25,
+                                chunk=chunk, value_div=2)
+        close(out2.cpu(), ref, tol)
 
 
 def test_one_far_key_among_hundreds_inside_a_long_window():
@@ -409,10 +411,13 @@ def test_head_difference_norm(dt, tol, H, rep, dv):
     n, lam, diff = 19, 0.37, 0.2
     buf = torch.randn(n, 2 * H * dv + 4, generator=g).to(dt)
     a = buf[:, :2 * H * dv].unflatten(1, (2 * H, dv))
-    out = M.head_diff_norm(a.to(DEV), lam, 1.0 - diff, 1e-5, rep)
     a64 = a.to(F64).reshape(n, H // rep, 2, rep, dv)               # (kv head, map, head in group)
     o = (a64[:, :, 0] - lam * a64[:, :, 1]).reshape(n, H, dv)
-    close(out.cpu(), (R.rms(o, 1e-5) * (1.0 - diff)).reshape(n, H * dv), tol)
+    want = (R.rms(o, 1e-5) * (1.0 - diff)).reshape(n, H * dv)
+    close(M.head_diff_norm(a.to(DEV), lam, 1.0 - diff, 1e-5, rep).cpu(), want, tol)
+    out = M.head_diff_norm(a.float().to(DEV), lam, 1.0 - diff, 1e-5, rep, dtype=dt)      # fp32 maps, rounded at the end
+    assert out.dtype == dt
+    close(out.cpu(), want, tol)
 
 
 @pytest.mark.parametrize("dt,tol", [(torch.float32, 2e-6), (torch.bfloat16, 2e-2)], ids=["fp32", "bf16"])
