@@ -265,6 +265,7 @@ struct AttnArgs {
   int row_heads = 0;   // tensor-core kernel, > 0: a tile is ONE token and its 16 rows are consecutive heads of `row_heads`
                        // that share one kv head; H then counts groups of 16 heads
   int out_f32 = 0;     // != 0: `out` is fp32 (same strides, in elements) whatever T is; plain outputs only (no turn back)
+  int stage_q = 0;     // tensor-core kernel: a warp's 16 query rows are staged in shared memory once (always with row_heads)
 };
 
 // first key a position sees (the kept first tokens of a window aside)
@@ -557,9 +558,11 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
   float* raw = reinterpret_cast<float*>(stage0 + stages * stage_elems);         // [H][16][40]
   float* talk_s = raw + (mixed ? H * kTcRows * kTcRawStride : 0);                               // [HC][H]
   const int RH = EXT ? A.row_heads : 0;
-  // heads on the rows: a warp's 16 query rows are staged once (a lone warp per CTA cannot hide their global latency)
+  // a warp's 16 query rows staged once: few resident warps cannot hide the latency of re-reading them for every key tile
+  // (heads on the rows: one warp per CTA; wide value layouts: one CTA per SM)
+  const bool QS = EXT && A.stage_q;
   T* q_s = reinterpret_cast<T*>(talk_s + (mixed ? HC * H : 0));                                 // [HC][16][dk + 8]
-  if (RH) {
+  if (QS) {
     const int kch = dk / 8;
     for (int hl = warp * HW; hl < warp * HW + HW; ++hl) {
       const int h = h0 + hl;
@@ -567,9 +570,11 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
       for (int e = lane; e < kTcRows * kch; e += 32) {
         const int r = e / kch, ch = e - r * kch;
         int4 v = make_int4(0, 0, 0, 0);
-        if (16 * h + r < RH)
-          v = *reinterpret_cast<const int4*>(static_cast<const T*>(A.q) + static_cast<int64_t>(row0) * A.q_tok_stride +
-                                             (16 * h + r) * A.q_head_stride + ch * 8);
+        const bool ok = RH ? 16 * h + r < RH : r < cnt;
+        if (ok)
+          v = *reinterpret_cast<const int4*>(static_cast<const T*>(A.q) +
+                                             (RH ? static_cast<int64_t>(row0) * A.q_tok_stride + (16 * h + r) * A.q_head_stride
+                                                 : static_cast<int64_t>(row0 + r) * A.q_tok_stride + h * A.q_head_stride) + ch * 8);
         *reinterpret_cast<int4*>(q_s + (hl * kTcRows + r) * ks + ch * 8) = v;
       }
     }
@@ -606,10 +611,10 @@ mixed_prompt_attn_kernel(const AttnArgs A, const int32_t* __restrict__ tiles, co
   auto scores = [&](int h, float (&s)[4][4]) {
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
-    // heads on the rows: the staged rows (rows past the heads are zero); else the query rows in global memory
-    const T* qa = RH ? q_s + ((h - h0) * kTcRows + qr) * ks + qc
+    // the staged rows (rows past the tile's are zero), else the query rows in global memory
+    const T* qa = QS ? q_s + ((h - h0) * kTcRows + qr) * ks + qc
                      : qbase + static_cast<int64_t>(row0 + qr) * A.q_tok_stride + h * A.q_head_stride + qc;
-    const T* qb = qa + 8 * (RH ? static_cast<int64_t>(ks) : A.q_tok_stride);
+    const T* qb = qa + 8 * (QS ? static_cast<int64_t>(ks) : A.q_tok_stride);
     const int rows = RH ? min(16, RH - 16 * h) : cnt;
     const bool va = qr < rows, vb = qr + 8 < rows;
     const T* kt = Ks + (h / rep - g_lo) * kTcKeys * ks + qr * ks + qc;
@@ -936,7 +941,7 @@ struct TcPlan {
 };
 
 inline bool tc_plan(int H, int G, int dk, int dv, bool has_talk, bool same_pool, bool unrotate, int dtype, TcPlan* plan,
-                    bool heads_as_rows = false) {
+                    bool stage_q = false) {
   if (dtype == B200_DTYPE_F32 || dk % 16 || dv % 8 || dv > 256 || H % G) return false;
   const int dv8 = dv <= 64 ? 8 : (dv <= 128 ? 16 : 32), dvp = dv8 * 8;
   // two heads per warp pay when the CTA's heads share what is staged: with a mixing matrix (all heads' raw scores are
@@ -949,7 +954,7 @@ inline bool tc_plan(int H, int G, int dk, int dv, bool has_talk, bool same_pool,
   if (!alias) stage += static_cast<size_t>(gs) * kTcKeys * (dvp + 8) * 2;
   size_t rest = 0;
   if (has_talk) rest = sizeof(float) * (static_cast<size_t>(H) * kTcRows * kTcRawStride + static_cast<size_t>(kTcWarps) * hw * H);
-  if (heads_as_rows) rest += static_cast<size_t>(kTcWarps) * hw * kTcRows * (dk + 8) * 2;   // the staged query rows
+  if (stage_q) rest += static_cast<size_t>(kTcWarps) * hw * kTcRows * (dk + 8) * 2;   // the staged query rows
   const size_t slab = unrotate ? sizeof(float) * kTcWarps * kTcRows * static_cast<size_t>(dvp) : 0;
   const size_t cap = 227 * 1024;
   int stages = 2;
@@ -1432,12 +1437,19 @@ int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_he
   if ((q_tok_stride | q_head_stride | out_tok_stride | out_head_stride) & 1)
     return fail(B200_ESHAPE, "b200_mixed_prompt_attn: odd strides");
   TcPlan plan;
-  if (!tc_plan(H, G, dk, dv, talk != nullptr, k_pool == v_pool, value_rot != nullptr, dtype, &plan, heads_as_rows != 0))
+  // query rows are staged where few warps are resident anyway: heads on the rows, and the widest value layout (one CTA
+  // per SM by its registers) when its rows allow 16-byte reads
+  const bool q_ok = aligned16(q) && !((q_tok_stride | q_head_stride) & 7);
+  const bool ext_call = chunk > 0 || v_div > 1 || v_row != dv || heads_as_rows || out_f32;
+  bool stage_q = heads_as_rows || (ext_call && dv > 128 && q_ok);
+  if (stage_q && !heads_as_rows && !tc_plan(H, G, dk, dv, talk != nullptr, k_pool == v_pool, value_rot != nullptr, dtype, &plan, true))
+    stage_q = false;
+  if (!tc_plan(H, G, dk, dv, talk != nullptr, k_pool == v_pool, value_rot != nullptr, dtype, &plan, stage_q))
     return fail(B200_ESHAPE, "b200_mixed_prompt_attn: sizes off the tensor-core grid (dk %d, dv %d)", dk, dv);
   AttnArgs A{out, out_tok_stride, out_head_stride, q, q_tok_stride, q_head_stride, gate, gate_stride, k_pool, v_pool,
              block_tables, table_stride, nullptr, tok_pos, talk, sink, scale, window, keep_first, value_rot != nullptr,
              interleaved, 0.0, H, G, dk, dv, block_size, softcap, chunk, v_row, v_div, heads_as_rows ? H_real : 0,
-             out_f32};
+             out_f32, stage_q ? 1 : 0};
   const dim3 grid(n_tiles, (H + kTcWarps * plan.hw - 1) / (kTcWarps * plan.hw), n_splits);
   return hybrid_by_dtype(dtype, "b200_mixed_prompt_attn", [&](auto* tag) {
     using T = std::remove_pointer_t<decltype(tag)>;
@@ -1451,7 +1463,7 @@ int b200_mixed_prompt_attn_ext(void* out, int64_t out_tok_stride, int64_t out_he
         cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
         kern<<<grid, kTcWarps * 32, plan.smem, s>>>(A, tiles, value_rot, workspace, n_tok, plan.stages);
       };
-      const bool ext = chunk > 0 || v_div > 1 || v_row != dv || heads_as_rows || out_f32;
+      const bool ext = ext_call;
       if (ext) {
         if (plan.dv8 == 8 && plan.hw == 1) launch(mixed_prompt_attn_kernel<T, 8, 1, true>);
         else if (plan.dv8 == 8) launch(mixed_prompt_attn_kernel<T, 8, 2, true>);

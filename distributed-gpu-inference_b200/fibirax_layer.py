@@ -251,12 +251,13 @@ class GroupedSoftmaxMoE(nn.Module):
         ids, w = self._route(x)
         # rows in expert order; where each expert's rows start comes from the sorted ids themselves (a search, not a
         # count: no value ever travels to the host)
-        sorted_ids, order = torch.sort(ids.reshape(-1).to(torch.int64), stable=True)
+        # 16-bit keys: the radix sort takes two passes where 64-bit keys take eight (expert counts stay far below 2^15)
+        sorted_ids, order = torch.sort(ids.reshape(-1).to(torch.int16), stable=True)
         where = torch.empty_like(order)
         where[order] = self._arange(n * top, h.device)
         ys = h.new_empty((0, h.shape[1]))
         if E:
-            offsets = torch.searchsorted(sorted_ids, self._arange(E + 1, h.device)).to(torch.int32)
+            offsets = torch.searchsorted(sorted_ids, self._arange(E + 1, h.device).to(torch.int16)).to(torch.int32)
             xs = mixer_ops.gather_rows(h, order, top)      # identity rows ride at the end and are never multiplied
             if self.grouped and n * top <= self.GROUPED_MAX_ROWS:
                 y = self._activate(mixer_ops.grouped_linear(xs, self.w_gu, offsets))
