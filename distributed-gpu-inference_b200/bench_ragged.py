@@ -592,7 +592,7 @@ def _vatazen_kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx, hbm, tf) -> D
             "mixed_paged_attention[latent]": lat,
             "mixed_prompt_attention[differential]": dif,
             "mixed_paged_attention[differential]": dif,
-            "head_diff_norm": (n_tok * Hd * dv * 6, 0),
+            "head_diff_norm": (n_tok * Hd * dv * 10, 0),      # two fp32 maps in, one 16-bit row out
             "gated_postnorm_residual": (n_tok * W * 14, 0),
             "relu_squared": (n_tok * top * s["eff"] * 4, 0),
             "gated_table_rows": (n_tok * VATAZEN_SIDE * 6, 0),
