@@ -211,6 +211,7 @@ MIXER_SIGNATURES = {
         c_int, [c_void_p, c_void_p, c_int64, c_int, c_void_p, c_int64, c_void_p, c_float, c_void_p, c_float, c_int, c_int,
                 c_int, c_void_p]),
     "b200_relu_squared": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_int, c_int, c_void_p]),
+    "b200_router_logits": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int, c_int, c_void_p]),
     "b200_gated_table_rows": (
         c_int, [c_void_p, c_void_p, c_int64, c_void_p, c_int64, c_int, c_void_p, c_int64, c_int, c_int, c_void_p]),
 }

@@ -596,6 +596,7 @@ def _vatazen_kernel_table(s, ev_prompt, ev_decode, B, Pn, Bd, ctx, hbm, tf) -> D
             "gated_postnorm_residual": (n_tok * W * 14, 0),
             "relu_squared": (n_tok * top * s["eff"] * 4, 0),
             "gated_table_rows": (n_tok * VATAZEN_SIDE * 6, 0),
+            "router_logits": (n_tok * W * 4, 0),
             "gather_rows": (n_tok * top * W * 4, 0),
             "weighted_expert_combine": (n_tok * top * W * 2 + n_tok * W * (4 + 4), 0),
         }

@@ -14,6 +14,7 @@
 //   squared ReLU                 y = max(z, 0)^2
 //   gated table rows             g = gelu_tanh(z) * table[token][col0 ...]: a per-layer slice of a second embedding table
 //                                gated by a projection of the residual
+//   router logits                fp32 x . W^T + b for few outputs, summed in an order that depends on the width alone
 //
 // Every size and constant of a design is a parameter.  Norm statistics, angles, gates and the residual are fp32 whatever
 // the storage dtype T is.
@@ -254,6 +255,60 @@ gated_table_rows_kernel(T* __restrict__ out, const T* __restrict__ z, int64_t z_
   }
 }
 
+// ---- router logits -------------------------------------------------------------------------------------------------
+// One CTA of four warps per token, kRouterChunk experts at a time: thread t owns columns t, t + 128, ... (four at a time
+// when the width allows); partial sums meet in a butterfly per warp and the four warps' sums are added in warp order.
+// The order of every sum depends on the width alone, so a token's logits - and with them its experts - do not depend on
+// what else the step carries.
+constexpr int kRouterChunk = 8;
+constexpr int kRouterThreads = 128;
+
+template <bool VEC>
+__global__ void __launch_bounds__(kRouterThreads)
+router_logits_kernel(float* __restrict__ logits, const float* __restrict__ x, const float* __restrict__ w,
+                     const float* __restrict__ bias, int E, int W) {
+  __shared__ float part[kRouterThreads / 32][kRouterChunk];
+  const int64_t n = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float* xr = x + n * W;
+  for (int e0 = 0; e0 < E; e0 += kRouterChunk) {
+    float acc[kRouterChunk];
+#pragma unroll
+    for (int j = 0; j < kRouterChunk; ++j) acc[j] = 0.f;
+    if (VEC) {
+      for (int i = threadIdx.x * 4; i < W; i += kRouterThreads * 4) {
+        const float4 xv = *reinterpret_cast<const float4*>(xr + i);
+#pragma unroll
+        for (int j = 0; j < kRouterChunk; ++j)
+          if (e0 + j < E) {
+            const float4 wv = *reinterpret_cast<const float4*>(w + static_cast<int64_t>(e0 + j) * W + i);
+            acc[j] = fmaf(xv.x, wv.x, fmaf(xv.y, wv.y, fmaf(xv.z, wv.z, fmaf(xv.w, wv.w, acc[j]))));
+          }
+      }
+    } else {
+      for (int i = threadIdx.x; i < W; i += kRouterThreads) {
+        const float xv = xr[i];
+#pragma unroll
+        for (int j = 0; j < kRouterChunk; ++j)
+          if (e0 + j < E) acc[j] = fmaf(xv, w[static_cast<int64_t>(e0 + j) * W + i], acc[j]);
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < kRouterChunk; ++j) {
+      const float t = warp_sum(acc[j]);
+      if (lane == 0) part[warp][j] = t;
+    }
+    __syncthreads();
+    if (threadIdx.x < kRouterChunk && e0 + threadIdx.x < E) {
+      float t = part[0][threadIdx.x];
+#pragma unroll
+      for (int ww = 1; ww < kRouterThreads / 32; ++ww) t += part[ww][threadIdx.x];
+      logits[n * E + e0 + threadIdx.x] = t + (bias ? bias[e0 + threadIdx.x] : 0.f);
+    }
+    __syncthreads();
+  }
+}
+
 }  // namespace
 }  // namespace b200
 
@@ -372,6 +427,20 @@ int b200_gated_table_rows(void* out, const void* z, int64_t z_stride, const void
         n_tok, d);
     return check_launch("b200_gated_table_rows");
   });
+}
+
+int b200_router_logits(float* logits, const float* x, const float* w, const float* bias, int64_t n_tok, int E, int width,
+                       void* stream) {
+  if (n_tok < 0 || E <= 0 || width <= 0) return fail(B200_EINVAL, "b200_router_logits: bad sizes");
+  if (n_tok == 0) return 0;
+  if (!logits || !x || !w) return fail(B200_EINVAL, "b200_router_logits: null pointer");
+  const unsigned grid = static_cast<unsigned>(n_tok);
+  auto s = static_cast<cudaStream_t>(stream);
+  if (width % 4 == 0 && aligned16(x) && aligned16(w))
+    router_logits_kernel<true><<<grid, kRouterThreads, 0, s>>>(logits, x, w, bias, E, width);
+  else
+    router_logits_kernel<false><<<grid, kRouterThreads, 0, s>>>(logits, x, w, bias, E, width);
+  return check_launch("b200_router_logits");
 }
 
 }  // extern "C"

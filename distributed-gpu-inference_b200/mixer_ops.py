@@ -916,3 +916,20 @@ def gated_table_rows(z: torch.Tensor, table: torch.Tensor, col0: int, tokens: to
                                        tokens.data_ptr(), n, d, DTYPE_ID[z.dtype], _stream())
     _lib.check_mixers(rc, "b200_gated_table_rows")
     return out
+
+
+@_timed
+def router_logits(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """fp32 ``x [n, width] @ w [E, width].T + bias``: a router's logits, every sum in an order fixed by the width (a
+    token's choice of experts does not depend on the rest of the step)."""
+    _need_cuda(x, w)
+    if x.dtype != torch.float32 or w.dtype != torch.float32 or x.dim() != 2 or w.dim() != 2 or x.shape[1] != w.shape[1] \
+            or not x.is_contiguous() or not w.is_contiguous():
+        raise ValueError("x [n, width] and w [E, width] are contiguous fp32")
+    if bias is not None and (bias.dtype != torch.float32 or bias.numel() != w.shape[0] or not bias.is_contiguous()):
+        raise ValueError("bias is contiguous fp32 [E]")
+    out = torch.empty((x.shape[0], w.shape[0]), dtype=torch.float32, device=x.device)
+    rc = _lib_().b200_router_logits(out.data_ptr(), x.data_ptr(), w.data_ptr(), _ptr(bias), x.shape[0], w.shape[0],
+                                    x.shape[1], _stream())
+    _lib.check_mixers(rc, "b200_router_logits")
+    return out

@@ -266,7 +266,7 @@ class SquaredReluMoE(GroupedSoftmaxMoE):
         self.ws_gu = self.ws_down = None
 
     def _route(self, x: torch.Tensor):
-        return mixer_ops.softmax_group_topk(F.linear(x, self.w_router, self.b_router), None, self.top)
+        return mixer_ops.softmax_group_topk(mixer_ops.router_logits(x, self.w_router, self.b_router), None, self.top)
 
     def _activate(self, z: torch.Tensor) -> torch.Tensor:
         return mixer_ops.relu_squared(z)

@@ -343,6 +343,11 @@ int b200_relu_squared(void* out, const void* z, int64_t z_stride, int64_t rows, 
 int b200_gated_table_rows(void* out, const void* z, int64_t z_stride, const void* table, int64_t table_stride, int col0,
                           const int64_t* tokens, int64_t n_tok, int d, int dtype, void* stream);
 
+/* logits[n, e] = sum_i x[n, i] * w[e, i] + bias[e] in fp32 (bias may be NULL): x fp32 [n_tok, width] and w fp32 [E, width]
+ * contiguous.  Meant for routers (few outputs); every sum runs in an order fixed by the width, whatever n_tok is. */
+int b200_router_logits(float* logits, const float* x, const float* w, const float* bias, int64_t n_tok, int E, int width,
+                       void* stream);
+
 #ifdef __cplusplus
 }
 #endif

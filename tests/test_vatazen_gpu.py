@@ -477,6 +477,19 @@ def test_routed_feed_forward_softmax_over_the_chosen(dt, spec, W):
     assert torch.allclose(w.sum(-1), torch.ones(9, dtype=F64)) and ids.shape == (9, 2)
 
 
+@pytest.mark.parametrize("n,E,W", [(45, 5, 56), (1, 1, 16), (300, 12, 200), (33, 40, 130), (9, 8, 2048)])
+def test_router_logits_do_not_depend_on_the_batch(n, E, W):
+    from dgi_b200 import mixer_ops as M
+
+    g = torch.Generator().manual_seed(n + E)
+    x, w, b = torch.randn(n, W, generator=g), torch.randn(E, W, generator=g), torch.randn(E, generator=g)
+    got = M.router_logits(x.to(DEV), w.to(DEV), b.to(DEV))
+    close(got.cpu(), x.to(F64) @ w.to(F64).T + b.to(F64), 2e-6 * W ** 0.5)
+    close(M.router_logits(x.to(DEV), w.to(DEV)).cpu(), x.to(F64) @ w.to(F64).T, 2e-6 * W ** 0.5)
+    one = M.router_logits(x[n // 2:n // 2 + 1].contiguous().to(DEV), w.to(DEV), b.to(DEV))      # a row alone: the same bits
+    assert torch.equal(one[0], got[n // 2])
+
+
 # ---- the model through the engine ----------------------------------------------------------------------------------
 @pytest.mark.parametrize("cfg", [CFG_A, CFG_B, CFG_C], ids=["A", "B", "C"])
 def test_whole_prompt_fp32(cfg):
